@@ -2,10 +2,15 @@
 //
 //   li_convert             dst = src between float and bfloat16 (rows may be column slices of wider tensors)
 //   li_layernorm           v = x[row] (+ w_d * norm(value[row]));  x[row] = v (optional);  out = w * norm(v)
-//                          norm(v) = (v - mean) / sqrt(var + eps), var = mean of squared deviations; one block a row
+//                          norm(v) = (v - mean) / sqrt(var + eps), var = mean of squared deviations; one block a row.
+//                          Either norm may be a root-mean-square norm instead (no mean taken off), out may be the
+//                          sum v itself (rounded to the engine's type: what a sublayer reads of a 32-bit stream
+//                          that is normalised only on its way back), and the weights may be 32-bit
 //   li_projection_rmsnorm  x = w * x / sqrt(mean(x^2) + eps) in place over whole rows of one or two neighbouring
 //                          column slices (q and k of a fused projection, each normalised across all its heads)
-//   li_gated_rmsnorm       out = w * x / sqrt(mean(x^2) + eps) * silu(gate) per head; one warp a (token, head)
+//   li_gated_rmsnorm       out = w * x / sqrt(mean(x^2) + eps) * act(gate) per head; one warp a (token, head);
+//                          act = silu or sigmoid; w shared by the heads or one per head; x optionally divided by
+//                          a number per (token, head) first
 //
 // x of li_layernorm may be float while value, weights and out are bfloat16: the stream stays 32-bit, what the
 // products read is rounded once.  Means, variances, the sum into the stream and every product before the final
@@ -44,12 +49,13 @@ __device__ __forceinline__ void row_statistics(const float* row, int width, floa
   inv = 1.0f / sqrtf(var + eps);
 }
 
-// T: dtype of value, the weights and out.  X: dtype of the stream x.
-template <typename T, typename X>
+// T: dtype of value and out.  X: dtype of the stream x.  W: dtype of the weights.  value_centre / centre: whether
+// the delta's norm / the norm of the sum takes the mean off; plain_out: out is the sum itself.
+template <typename T, typename X, typename W>
 __global__ void __launch_bounds__(1024)
-layernorm_kernel(X* __restrict__ x, const T* __restrict__ value, const T* __restrict__ value_weight,
-                 const T* __restrict__ weight, T* __restrict__ out, const int* __restrict__ rows, int width, float eps,
-                 float value_eps, int write_stream, int centre) {
+layernorm_kernel(X* __restrict__ x, const T* __restrict__ value, const W* __restrict__ value_weight,
+                 const W* __restrict__ weight, T* __restrict__ out, const int* __restrict__ rows, int width, float eps,
+                 float value_eps, int write_stream, int centre, int value_centre, int plain_out) {
   extern __shared__ float row[];  // [width]
   __shared__ float scratch[33];
   grid_dependency_wait();
@@ -59,7 +65,7 @@ layernorm_kernel(X* __restrict__ x, const T* __restrict__ value, const T* __rest
   if (value != nullptr) {
     for (int c = threadIdx.x; c < width; c += blockDim.x) row[c] = to_float(value[at + c]);
     __syncthreads();
-    row_statistics(row, width, value_eps, true, scratch, mean, inv);
+    row_statistics(row, width, value_eps, value_centre != 0, scratch, mean, inv);
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
       const float normed = (row[c] - mean) * inv * to_float(value_weight[c]);
       const float v = to_float(x[at + c]) + normed;
@@ -71,8 +77,12 @@ layernorm_kernel(X* __restrict__ x, const T* __restrict__ value, const T* __rest
   }
   if (out == nullptr) return;
   __syncthreads();
-  row_statistics(row, width, eps, centre != 0, scratch, mean, inv);
   T* o = out + (size_t)r * width;
+  if (plain_out) {
+    for (int c = threadIdx.x; c < width; c += blockDim.x) o[c] = from_float<T>(row[c]);
+    return;
+  }
+  row_statistics(row, width, eps, centre != 0, scratch, mean, inv);
   for (int c = threadIdx.x; c < width; c += blockDim.x) o[c] = from_float<T>((row[c] - mean) * inv * to_float(weight[c]));
 }
 
@@ -99,11 +109,11 @@ __device__ __forceinline__ void store4(bf16* p, const float (&v)[4]) {
 
 // The same norm with the row in registers: thread i keeps the four-element chunks i, i + blockDim, ... (NV of them).
 // For widths that are multiples of four and at most 4 * NV * blockDim, and 16-byte aligned rows.
-template <typename T, typename X, int NV>
+template <typename T, typename X, typename W, int NV>
 __global__ void __launch_bounds__(1024)
-layernorm_rows_kernel(X* __restrict__ x, const T* __restrict__ value, const T* __restrict__ value_weight,
-                      const T* __restrict__ weight, T* __restrict__ out, const int* __restrict__ rows, int width,
-                      float eps, float value_eps, int write_stream, int centre) {
+layernorm_rows_kernel(X* __restrict__ x, const T* __restrict__ value, const W* __restrict__ value_weight,
+                      const W* __restrict__ weight, T* __restrict__ out, const int* __restrict__ rows, int width,
+                      float eps, float value_eps, int write_stream, int centre, int value_centre, int plain_out) {
   __shared__ float scratch[33];
   // The weights are inputs of the model, not of a kernel: they are on their way before the wait.
   float w[NV][4], wd[NV][4];
@@ -112,7 +122,7 @@ layernorm_rows_kernel(X* __restrict__ x, const T* __restrict__ value, const T* _
   for (int i = 0; i < NV; ++i) {
     col[i] = (i * blockDim.x + threadIdx.x) * 4;
     if (col[i] < width) {
-      if (weight != nullptr) load4(weight + col[i], w[i]);
+      if (weight != nullptr && !plain_out) load4(weight + col[i], w[i]);
       if (value != nullptr) load4(value_weight + col[i], wd[i]);
     }
   }
@@ -130,7 +140,7 @@ layernorm_rows_kernel(X* __restrict__ x, const T* __restrict__ value, const T* _
         s += (v[i][0] + v[i][1]) + (v[i][2] + v[i][3]);
       }
     }
-    const float mean = block_sum(s, scratch) / n;
+    const float mean = value_centre ? block_sum(s, scratch) / n : 0.f;
     float q = 0.f;
 #pragma unroll
     for (int i = 0; i < NV; ++i)
@@ -159,6 +169,12 @@ layernorm_rows_kernel(X* __restrict__ x, const T* __restrict__ value, const T* _
       if (col[i] < width) load4(x + at + col[i], v[i]);
   }
   if (out == nullptr) return;
+  if (plain_out) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+      if (col[i] < width) store4(out + (size_t)r * width + col[i], v[i]);
+    return;
+  }
   float mean = 0.f;
   if (centre) {
     float s = 0.f;
@@ -206,10 +222,12 @@ projection_rmsnorm_kernel(T* __restrict__ x, size_t stride, int width_a, const T
   for (int c = threadIdx.x; c < width; c += blockDim.x) p[c] = from_float<T>(to_float(p[c]) * inv * to_float(w[c]));
 }
 
+// weight_stride: 0 = one weight vector for every head, `size` = one per head.  act: 0 silu, 1 sigmoid.  den (may
+// be null): x[t, h] is divided by den[t * heads + h] before anything else.
 template <typename T>
 __global__ void gated_rmsnorm_kernel(const float* __restrict__ x, const T* __restrict__ gate, size_t gate_stride,
                                      const float* __restrict__ weight, T* __restrict__ out, int tokens, int heads,
-                                     int size, float eps) {
+                                     int size, float eps, int weight_stride, int act, const float* __restrict__ den) {
   grid_dependency_wait();
   const int lane = threadIdx.x & 31;
   const size_t item = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);   // (token, head)
@@ -217,14 +235,21 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ x, const T* __res
   const size_t t = item / heads;
   const int h = (int)(item - t * heads);
   const float* xr = x + (t * heads + h) * size;
+  const float under = den != nullptr ? den[item] : 1.0f;
   float q = 0.f;
-  for (int c = lane; c < size; c += 32) q += xr[c] * xr[c];
+  for (int c = lane; c < size; c += 32) {
+    const float v = den != nullptr ? xr[c] / under : xr[c];
+    q += v * v;
+  }
   const float inv = 1.0f / sqrtf(warp_sum(q) / (float)size + eps);
   const T* g = gate + t * gate_stride + (size_t)h * size;
+  const float* w = weight + (size_t)h * weight_stride;
   T* o = out + (t * heads + h) * size;
   for (int c = lane; c < size; c += 32) {
     const float z = to_float(g[c]);
-    o[c] = from_float<T>(xr[c] * inv * weight[c] * (z / (1.0f + expf(-z))));
+    const float s = 1.0f / (1.0f + expf(-z));
+    const float v = den != nullptr ? xr[c] / under : xr[c];
+    o[c] = from_float<T>(v * inv * w[c] * (act == 1 ? s : z * s));
   }
 }
 
@@ -251,18 +276,21 @@ LI_EXPORT int li_convert(int src_dtype, const void* src, size_t src_stride, int 
   return convert_from<bf16>(dst_dtype, src, src_stride, dst, dst_stride, rows, width, grid, stream);
 }
 
-// dtype: of value, value_weight, weight and out.  x_dtype: of the stream x.  flags: 1 = store the sum back into
-// x, 2 = the norm of the sum is not centred (a root-mean-square norm).  value == null: no delta.  out == null:
+// dtype: of value and out.  x_dtype: of the stream x.  w_dtype: of value_weight and weight (dtype, or float32).
+// flags: 1 = store the sum back into x, 2 = the norm of the sum is not centred (a root-mean-square norm), 4 = the
+// delta's norm is not centred, 8 = out is the sum itself, not its norm.  value == null: no delta.  out == null:
 // only the sum is made.
 LI_EXPORT int li_layernorm(int dtype, void* x, int x_dtype, const void* value, const void* value_weight,
                            const void* weight, void* out, const int* rows, int n, int width, float eps,
-                           float value_eps, int flags, cudaStream_t stream) {
+                           float value_eps, int flags, int w_dtype, cudaStream_t stream) {
   if (n <= 0) return 0;
   if (width < 1 || (size_t)width * sizeof(float) > 200 * 1024) return LI_ERR_UNSUPPORTED;
-  if (dtype == kFloat32 && x_dtype != kFloat32) return LI_ERR_UNSUPPORTED;
+  if (dtype == kFloat32 && (x_dtype != kFloat32 || w_dtype != kFloat32)) return LI_ERR_UNSUPPORTED;
+  if (w_dtype != dtype && (w_dtype != kFloat32 || x_dtype != kFloat32)) return LI_ERR_UNSUPPORTED;
   const size_t smem = (size_t)width * sizeof(float);
   const int threads = width >= 4096 ? 1024 : width >= 1024 ? 512 : 256;
-  const int write_stream = flags & 1, centre = (flags & 2) ? 0 : 1;
+  const int write_stream = flags & 1, centre = (flags & 2) ? 0 : 1, value_centre = (flags & 4) ? 0 : 1;
+  const int plain_out = (flags & 8) ? 1 : 0;
   // Rows of up to 16,384 elements that 16-byte accesses can walk stay in registers.
   const bool in_registers = width % 4 == 0 && width <= 16384 && aligned16(x) && aligned16(value) && aligned16(out) &&
                             aligned16(weight) && aligned16(value_weight);
@@ -270,35 +298,38 @@ LI_EXPORT int li_layernorm(int dtype, void* x, int x_dtype, const void* value, c
     const int quads = width / 4;
     const int block = quads >= 1024 ? 1024 : ((quads + 31) / 32) * 32;
     const int per_thread = (quads + block - 1) / block;
-#define LI_LAUNCH_ROWS(T, X, NV)                                                                                      \
-  return (int)launch_pdl(n, layernorm_rows_kernel<T, X, NV>, dim3(n), dim3(block), 0, stream, (X*)x, (const T*)value,  \
-                         (const T*)value_weight, (const T*)weight, (T*)out, rows, width, eps, value_eps, write_stream, \
-                         centre)
-#define LI_LAUNCH_ROWS_NV(T, X)                                                                                       \
+#define LI_LAUNCH_ROWS(T, X, W, NV)                                                                                   \
+  return (int)launch_pdl(n, layernorm_rows_kernel<T, X, W, NV>, dim3(n), dim3(block), 0, stream, (X*)x,               \
+                         (const T*)value, (const W*)value_weight, (const W*)weight, (T*)out, rows, width, eps,        \
+                         value_eps, write_stream, centre, value_centre, plain_out)
+#define LI_LAUNCH_ROWS_NV(T, X, W)                                                                                    \
   {                                                                                                                   \
-    if (per_thread == 1) LI_LAUNCH_ROWS(T, X, 1);                                                                     \
-    if (per_thread == 2) LI_LAUNCH_ROWS(T, X, 2);                                                                     \
-    LI_LAUNCH_ROWS(T, X, 4);                                                                                          \
+    if (per_thread == 1) LI_LAUNCH_ROWS(T, X, W, 1);                                                                  \
+    if (per_thread == 2) LI_LAUNCH_ROWS(T, X, W, 2);                                                                  \
+    LI_LAUNCH_ROWS(T, X, W, 4);                                                                                       \
   }
-    if (dtype == kFloat32) LI_LAUNCH_ROWS_NV(float, float)
-    if (x_dtype == kFloat32) LI_LAUNCH_ROWS_NV(bf16, float)
-    LI_LAUNCH_ROWS_NV(bf16, bf16)
+    if (dtype == kFloat32) LI_LAUNCH_ROWS_NV(float, float, float)
+    if (w_dtype == kFloat32) LI_LAUNCH_ROWS_NV(bf16, float, float)
+    if (x_dtype == kFloat32) LI_LAUNCH_ROWS_NV(bf16, float, bf16)
+    LI_LAUNCH_ROWS_NV(bf16, bf16, bf16)
 #undef LI_LAUNCH_ROWS_NV
 #undef LI_LAUNCH_ROWS
   }
-#define LI_LAUNCH_NORM(T, X)                                                                                          \
+#define LI_LAUNCH_NORM(T, X, W)                                                                                       \
   {                                                                                                                   \
     if (smem > 48 * 1024) {                                                                                           \
-      cudaError_t e = cudaFuncSetAttribute(layernorm_kernel<T, X>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      cudaError_t e = cudaFuncSetAttribute(layernorm_kernel<T, X, W>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
+                                           (int)smem);                                                                \
       if (e != cudaSuccess) return (int)e;                                                                            \
     }                                                                                                                 \
-    return (int)launch_pdl(n, layernorm_kernel<T, X>, dim3(n), dim3(threads), smem, stream, (X*)x, (const T*)value,   \
-                           (const T*)value_weight, (const T*)weight, (T*)out, rows, width, eps, value_eps,            \
-                           write_stream, centre);                                                                     \
+    return (int)launch_pdl(n, layernorm_kernel<T, X, W>, dim3(n), dim3(threads), smem, stream, (X*)x,                 \
+                           (const T*)value, (const W*)value_weight, (const W*)weight, (T*)out, rows, width, eps,      \
+                           value_eps, write_stream, centre, value_centre, plain_out);                                 \
   }
-  if (dtype == kFloat32) LI_LAUNCH_NORM(float, float)
-  if (x_dtype == kFloat32) LI_LAUNCH_NORM(bf16, float)
-  LI_LAUNCH_NORM(bf16, bf16)
+  if (dtype == kFloat32) LI_LAUNCH_NORM(float, float, float)
+  if (w_dtype == kFloat32) LI_LAUNCH_NORM(bf16, float, float)
+  if (x_dtype == kFloat32) LI_LAUNCH_NORM(bf16, float, bf16)
+  LI_LAUNCH_NORM(bf16, bf16, bf16)
 #undef LI_LAUNCH_NORM
 }
 
@@ -317,15 +348,17 @@ LI_EXPORT int li_projection_rmsnorm(int dtype, void* x, size_t stride, int rows,
 }
 
 LI_EXPORT int li_gated_rmsnorm(int dtype, const float* x, const void* gate, size_t gate_stride, const float* weight,
-                               void* out, int tokens, int heads, int size, float eps, cudaStream_t stream) {
+                               void* out, int tokens, int heads, int size, float eps, int weight_per_head, int act,
+                               const float* den, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (heads < 1 || size < 1) return LI_ERR_UNSUPPORTED;
+  if (heads < 1 || size < 1 || act < 0 || act > 1) return LI_ERR_UNSUPPORTED;
   const size_t items = (size_t)tokens * heads;
   const int warps = 8;
+  const int weight_stride = weight_per_head ? size : 0;
   const dim3 grid((unsigned)((items + warps - 1) / warps));
   if (dtype == kFloat32)
     return (int)launch_pdl(tokens, gated_rmsnorm_kernel<float>, grid, dim3(warps * 32), 0, stream, x, (const float*)gate,
-                           gate_stride, weight, (float*)out, tokens, heads, size, eps);
+                           gate_stride, weight, (float*)out, tokens, heads, size, eps, weight_stride, act, den);
   return (int)launch_pdl(tokens, gated_rmsnorm_kernel<bf16>, grid, dim3(warps * 32), 0, stream, x, (const bf16*)gate,
-                         gate_stride, weight, (bf16*)out, tokens, heads, size, eps);
+                         gate_stride, weight, (bf16*)out, tokens, heads, size, eps, weight_stride, act, den);
 }

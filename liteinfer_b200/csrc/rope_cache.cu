@@ -16,9 +16,104 @@
 // A page holds `page_size` tokens of every KV head: pool[page][kv_head][slot][dim].
 // The page of a token is block_table[seq][position / page_size]; a negative entry
 // (a page already given back) skips the write.
+//
+// li_head_norm_rope_kv_write does the same for an attention whose q and k pass a root-mean-square norm per head
+// before the rotation (one weight vector of head_dim for all q heads, one for all k heads), and whose values may
+// be blended with another layer's values of the same token before they are stored:
+//     q_h <- rot(w_q * q_h / sqrt(mean(q_h^2) + eps));  k likewise;  v <- (1 - lambda) v + lambda v_other
+// The row may be wider than q, k and v (further columns of a fused projection follow them).  Statistics, the
+// blend and the rotation are 32-bit; each result is rounded once.
+//
+// li_sigmoid_gate_heads multiplies head h of every row of x by sigmoid(gate[row, h]) in place.
 #include "common.cuh"
 
 namespace li {
+
+constexpr int kPrepWarps = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(kPrepWarps * 32)
+head_norm_rope_kv_write_kernel(T* __restrict__ qkv, size_t row_stride, const int* __restrict__ positions,
+                               const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
+                               int table_stride, T* __restrict__ k_pool, T* __restrict__ v_pool,
+                               const float* __restrict__ inv_freq, int heads, int kv_heads, int head_dim,
+                               int rotary_dim, int page_size, int num_pages, int v_dim,
+                               const T* __restrict__ q_norm, const T* __restrict__ k_norm, float norm_eps,
+                               const T* __restrict__ v_other, size_t v_other_stride,
+                               const float* __restrict__ lambda) {
+  extern __shared__ float shared[];  // cos[half], sin[half], then one head per warp
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  grid_launch_dependents();
+  const int pos = positions[t];
+  const int half = rotary_dim / 2;
+  float* cosv = shared;
+  float* sinv = shared + half;
+  float* head = shared + rotary_dim + warp * head_dim;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    const float angle = __fmul_rn((float)pos, inv_freq[i]);
+    cosv[i] = cosf(angle);
+    sinv[i] = sinf(angle);
+  }
+  const int seq = seq_of_token[t];
+  const int page = seq < 0 ? -1 : block_table[(size_t)seq * table_stride + pos / page_size];
+  const bool store = page >= 0 && page < num_pages;
+  const int slot = pos % page_size;
+  const float mix = lambda != nullptr ? lambda[0] : 0.f;
+  grid_dependency_wait();           // q, k and v come from the projection before this kernel
+  __syncthreads();
+
+  T* row = qkv + (size_t)t * row_stride;
+  for (int h = warp; h < heads + kv_heads; h += kPrepWarps) {
+    const bool is_q = h < heads;
+    const T* w = is_q ? q_norm : k_norm;
+    T* p = row + (size_t)h * head_dim;
+    float ss = 0.f;
+    for (int j = lane; j < head_dim; j += 32) {
+      const float x = to_float(p[j]);
+      head[j] = x;
+      ss = fmaf(x, x, ss);
+    }
+    if (w != nullptr) {
+      const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)head_dim + norm_eps);
+      for (int j = lane; j < head_dim; j += 32) head[j] = head[j] * inv * to_float(w[j]);
+    }
+    __syncwarp();
+    T* dst = is_q ? p : k_pool + (((size_t)page * kv_heads + (h - heads)) * page_size + slot) * head_dim;
+    if (is_q || store) {
+      for (int j = lane; j < head_dim; j += 32) {
+        float r;
+        if (j < half) r = rotate_lo(head[j], head[j + half], cosv[j], sinv[j]);
+        else if (j < rotary_dim) r = rotate_hi(head[j - half], head[j], cosv[j - half], sinv[j - half]);
+        else r = head[j];
+        dst[j] = from_float<T>(r);
+      }
+    }
+    __syncwarp();
+  }
+  if (!store) return;
+  const T* vrow = row + (size_t)(heads + kv_heads) * head_dim;
+  const T* orow = v_other != nullptr ? v_other + (size_t)t * v_other_stride : nullptr;
+  for (int w = threadIdx.x; w < kv_heads * v_dim; w += blockDim.x) {
+    const int h = w / v_dim, j = w - h * v_dim;
+    float v = to_float(vrow[w]);
+    if (orow != nullptr) v = fmaf(mix, to_float(orow[w]), (1.0f - mix) * v);
+    v_pool[(((size_t)page * kv_heads + h) * page_size + slot) * v_dim + j] = from_float<T>(v);
+  }
+}
+
+template <typename T>
+__global__ void sigmoid_gate_heads_kernel(T* __restrict__ x, const T* __restrict__ gate, size_t gate_stride,
+                                          size_t tokens, int heads, int size) {
+  grid_dependency_wait();
+  const size_t width = (size_t)heads * size, total = tokens * width;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / width;
+    const int h = (int)((i - t * width) / size);
+    const float g = to_float(gate[t * gate_stride + h]);
+    x[i] = from_float<T>(to_float(x[i]) * (1.0f / (1.0f + expf(-g))));
+  }
+}
 
 template <typename T>
 __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
@@ -165,4 +260,47 @@ LI_EXPORT int li_rope_kv_write(int dtype, void* qkv, const int* positions, const
   return (int)launch_pdl(tokens, rope_kv_write_kernel<bf16>, dim3(tokens), dim3(block), smem, stream, (bf16*)qkv, positions,
                          seq_of_token, block_table, table_stride, (bf16*)k_pool, (bf16*)v_pool, inv_freq, heads,
                          kv_heads, head_dim, rotary_dim, page_size, num_pages, v_dim, cs_scale);
+}
+
+// q_norm / k_norm: null = that projection is not normalised.  v_other with lambda: the stored values are
+// (1 - lambda[0]) v + lambda[0] v_other[t]; null = v as it is.  num_pages 0: nothing is stored (q is still
+// normalised and rotated).
+LI_EXPORT int li_head_norm_rope_kv_write(int dtype, void* qkv, size_t row_stride, const int* positions,
+                                         const int* seq_of_token, const int* block_table, int table_stride,
+                                         void* k_pool, void* v_pool, const float* inv_freq, int tokens, int heads,
+                                         int kv_heads, int head_dim, int rotary_dim, int page_size, int num_pages,
+                                         int v_dim, const void* q_norm, const void* k_norm, float norm_eps,
+                                         const void* v_other, size_t v_other_stride, const float* lambda,
+                                         cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  if (v_dim < 1 || head_dim < 1) return LI_ERR_UNSUPPORTED;
+  if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return LI_ERR_UNSUPPORTED;
+  if (rotary_dim > 0 && inv_freq == nullptr) return LI_ERR_UNSUPPORTED;
+  if ((v_other == nullptr) != (lambda == nullptr)) return LI_ERR_UNSUPPORTED;
+  const size_t smem = ((size_t)rotary_dim + (size_t)kPrepWarps * head_dim) * sizeof(float);
+  if (smem > 48 * 1024) return LI_ERR_UNSUPPORTED;
+  if (dtype == kFloat32)
+    return (int)launch_pdl(tokens, head_norm_rope_kv_write_kernel<float>, dim3(tokens), dim3(kPrepWarps * 32), smem,
+                           stream, (float*)qkv, row_stride, positions, seq_of_token, block_table, table_stride,
+                           (float*)k_pool, (float*)v_pool, inv_freq, heads, kv_heads, head_dim, rotary_dim, page_size,
+                           num_pages, v_dim, (const float*)q_norm, (const float*)k_norm, norm_eps,
+                           (const float*)v_other, v_other_stride, lambda);
+  return (int)launch_pdl(tokens, head_norm_rope_kv_write_kernel<bf16>, dim3(tokens), dim3(kPrepWarps * 32), smem, stream,
+                         (bf16*)qkv, row_stride, positions, seq_of_token, block_table, table_stride, (bf16*)k_pool,
+                         (bf16*)v_pool, inv_freq, heads, kv_heads, head_dim, rotary_dim, page_size, num_pages, v_dim,
+                         (const bf16*)q_norm, (const bf16*)k_norm, norm_eps, (const bf16*)v_other, v_other_stride,
+                         lambda);
+}
+
+LI_EXPORT int li_sigmoid_gate_heads(int dtype, void* x, const void* gate, size_t gate_stride, int tokens, int heads,
+                                    int size, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (heads < 1 || size < 1) return LI_ERR_UNSUPPORTED;
+  const size_t total = (size_t)tokens * heads * size;
+  const dim3 grid((unsigned)((total + 255) / 256 < 8192 ? (total + 255) / 256 : 8192));
+  if (dtype == kFloat32)
+    return (int)launch_pdl(tokens, sigmoid_gate_heads_kernel<float>, grid, dim3(256), 0, stream, (float*)x,
+                           (const float*)gate, gate_stride, (size_t)tokens, heads, size);
+  return (int)launch_pdl(tokens, sigmoid_gate_heads_kernel<bf16>, grid, dim3(256), 0, stream, (bf16*)x,
+                         (const bf16*)gate, gate_stride, (size_t)tokens, heads, size);
 }

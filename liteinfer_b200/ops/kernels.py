@@ -47,16 +47,24 @@ _SIGNATURES = {
     "li_rope_kv_write": ("rope_cache", [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                         c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                         c_void_p]),
+    "li_head_norm_rope_kv_write": ("rope_cache", [c_int, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p, c_int,
+                                                  c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                                  c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p,
+                                                  c_size_t, c_void_p, c_void_p]),
+    "li_sigmoid_gate_heads": ("rope_cache", [c_int, c_void_p, c_void_p, c_size_t, c_int, c_int, c_int, c_void_p]),
+    "li_mlstm": ("mlstm", [c_int, c_void_p, c_size_t, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
+                           c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
+                           c_int, c_void_p]),
     "li_paged_attention_generic": ("attention_generic", [
         c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_float, c_void_p]),
     "li_convert": ("layernorm", [c_int, c_void_p, c_size_t, c_int, c_void_p, c_size_t, c_int, c_int, c_void_p]),
     "li_layernorm": ("layernorm", [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                   c_int, c_int, c_float, c_float, c_int, c_void_p]),
+                                   c_int, c_int, c_float, c_float, c_int, c_int, c_void_p]),
     "li_projection_rmsnorm": ("layernorm", [c_int, c_void_p, c_size_t, c_int, c_int, c_void_p, c_int, c_void_p,
                                             c_float, c_void_p]),
     "li_gated_rmsnorm": ("layernorm", [c_int, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p, c_int, c_int, c_int,
-                                       c_float, c_void_p]),
+                                       c_float, c_int, c_int, c_void_p, c_void_p]),
     "li_short_conv": ("delta_rule", [c_int, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                      c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "li_short_conv_update": ("delta_rule", [c_int, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p, c_int, c_int,
@@ -672,6 +680,57 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, seq_of_token: torc
            "rope_kv_write")
 
 
+def head_norm_rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
+                            block_table: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                            inv_freq: torch.Tensor | None, heads: int, kv_heads: int, head_dim: int, rotary_dim: int,
+                            q_norm: torch.Tensor | None, k_norm: torch.Tensor | None, norm_eps: float,
+                            store: bool = True, v_other: torch.Tensor | None = None,
+                            blend: torch.Tensor | None = None) -> None:
+    """`rope_kv_write` for an attention whose q and k pass a root-mean-square norm per head first: every q head
+    becomes rot(q_norm * q / sqrt(mean(q^2) + eps)) in place, every k head likewise (with k_norm) on its way into
+    its page; None leaves that projection unnormalised.  q_norm and k_norm: [head_dim], the dtype of qkv.
+
+    qkv [tokens, >= (heads + kv_heads) * head_dim + kv_heads * v_dim]: q, k, v side by side at the start of each
+    row (further columns may follow; v_dim is the value pool's last axis).  `v_other` [tokens, kv_heads * v_dim]
+    (a column slice is fine) with `blend` (one float32 on the device): what is stored is
+    (1 - blend) * v + blend * v_other, computed in 32-bit and rounded once."""
+    _rows2d(qkv, "qkv")
+    _on_gpu(positions, seq_of_token, block_table, k_pool, v_pool, inv_freq, q_norm, k_norm, blend)
+    _int32(positions, "positions"); _int32(seq_of_token, "seq_of_token"); _int32(block_table, "block_table")
+    tokens = qkv.shape[0]
+    pages, kvh, page_size, hd = k_pool.shape
+    vd = v_pool.shape[-1]
+    assert (kvh, hd) == (kv_heads, head_dim) and v_pool.shape == (pages, kv_heads, page_size, vd)
+    assert qkv.shape[1] >= (heads + kv_heads) * head_dim + kv_heads * vd
+    assert k_pool.dtype == qkv.dtype == v_pool.dtype
+    assert inv_freq is None or (inv_freq.dtype == torch.float32 and inv_freq.numel() * 2 == rotary_dim)
+    for w in (q_norm, k_norm):
+        assert w is None or (w.numel() == head_dim and w.dtype == qkv.dtype)
+    assert (v_other is None) == (blend is None)
+    if v_other is not None:
+        _rows2d(v_other, "v_other")
+        assert v_other.shape == (tokens, kv_heads * vd) and v_other.dtype == qkv.dtype
+        assert blend.dtype == torch.float32 and blend.numel() == 1
+    _check(_fn("li_head_norm_rope_kv_write")(
+        _code(qkv), qkv.data_ptr(), qkv.stride(0), positions.data_ptr(), seq_of_token.data_ptr(),
+        block_table.data_ptr(), block_table.stride(0), k_pool.data_ptr(), v_pool.data_ptr(), _ptr(inv_freq), tokens,
+        heads, kv_heads, head_dim, rotary_dim if inv_freq is not None else 0, page_size, pages if store else 0, vd,
+        _ptr(q_norm), _ptr(k_norm), float(norm_eps), _ptr(v_other), v_other.stride(0) if v_other is not None else 0,
+        _ptr(blend), _stream()), "head_norm_rope_kv_write")
+
+
+def sigmoid_gate_heads_(x: torch.Tensor, gate: torch.Tensor, heads: int) -> torch.Tensor:
+    """x[t, h, :] *= sigmoid(gate[t, h]) in place: x [tokens, heads * size], gate [tokens, heads] (a column
+    slice is fine), both in the engine's dtype; the sigmoid and the product are 32-bit."""
+    _on_gpu(x)
+    _rows2d(gate, "gate")
+    tokens, width = x.shape
+    assert width % heads == 0 and gate.shape == (tokens, heads) and gate.dtype == x.dtype
+    _check(_fn("li_sigmoid_gate_heads")(_code(x), x.data_ptr(), gate.data_ptr(), gate.stride(0), tokens, heads,
+                                        width // heads, _stream()), "sigmoid_gate_heads")
+    return x
+
+
 _decode_capacity: dict[tuple[int, bool], int] = {}
 
 
@@ -895,12 +954,15 @@ def paged_attention(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_poo
 # ------------------------------------------------- 32-bit stream, layer norm, recurrences
 @dataclass
 class NormedDelta:
-    """A delta of the residual stream that has not been computed yet: weight * layer_norm(value), the output of a
-    sublayer that is normalised before it is added.  The norm that reads the stream next adds it on its way."""
+    """A delta of the residual stream that has not been computed yet: weight * norm(value), the output of a
+    sublayer that is normalised before it is added.  The norm that reads the stream next adds it on its way.
+    `centred`: a layer norm (the mean is taken off); otherwise a root-mean-square norm.  The weight has the
+    dtype of the value, or float32."""
 
     value: torch.Tensor
     weight: torch.Tensor
     eps: float
+    centred: bool = True
 
 
 def _rows2d(t: torch.Tensor, what: str) -> None:
@@ -925,34 +987,41 @@ def layernorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tens
               delta: "NormedDelta | None" = None, rows: torch.Tensor | None = None,
               write_stream: bool = False, centre: bool = True) -> torch.Tensor:
     """out[r] = weight * norm(v), v = x[row] (+ delta.weight * norm(delta.value[row])), row = rows[r] if given else r;
-    norm(v) = (v - mean) / sqrt(var + eps) (with `centre` False: v / sqrt(mean(v^2) + eps)).  With `write_stream`
-    v is stored back into x.  x may be float32 whatever the dtype of out and the weights (a 32-bit residual
-    stream); every statistic and the sum are 32-bit."""
+    norm(v) = (v - mean) / sqrt(var + eps) (with `centre` False: v / sqrt(mean(v^2) + eps); the delta's own norm
+    likewise by `delta.centred`).  With `write_stream` v is stored back into x.  x may be float32 whatever the
+    dtype of out (a 32-bit residual stream), and so may the weights; every statistic and the sum are 32-bit."""
     _on_gpu(x, weight, out, rows, delta.value if delta else None, delta.weight if delta else None)
     _int32(rows, "rows")
     width = x.shape[-1]
     n = out.shape[0]
-    assert weight.numel() == width and out.shape[-1] == width and out.dtype == weight.dtype
+    assert weight.numel() == width and out.shape[-1] == width and weight.dtype in (out.dtype, torch.float32)
     assert x.dtype in (torch.float32, out.dtype)
     assert rows is None or rows.numel() == n
     assert rows is not None or n == x.shape[0]
     assert delta is None or (delta.value.shape == x.shape and delta.value.dtype == out.dtype
-                             and delta.weight.dtype == out.dtype)
+                             and delta.weight.dtype == weight.dtype)
     assert not (write_stream and (delta is None or rows is not None))
+    flags = int(write_stream) | (0 if centre else 2) | (0 if delta is None or delta.centred else 4)
     _check(_fn("li_layernorm")(_code(out), x.data_ptr(), _code(x), _ptr(delta.value if delta else None),
                                _ptr(delta.weight if delta else None), weight.data_ptr(), out.data_ptr(), _ptr(rows),
-                               n, width, float(eps), float(delta.eps if delta else 0.0),
-                               int(write_stream) | (0 if centre else 2), _stream()), "layernorm")
+                               n, width, float(eps), float(delta.eps if delta else 0.0), flags, _code(weight),
+                               _stream()), "layernorm")
     return out
 
 
-def layernorm_add(stream: torch.Tensor, value: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
-    """stream += weight * layer_norm(value): `stream` float32 or the dtype of value; summed in 32-bit."""
-    _on_gpu(stream, value, weight)
-    assert stream.shape == value.shape and value.dtype == weight.dtype and stream.dtype in (torch.float32, value.dtype)
+def layernorm_add(stream: torch.Tensor, value: torch.Tensor, weight: torch.Tensor, eps: float,
+                  centred: bool = True, out: torch.Tensor | None = None) -> torch.Tensor:
+    """stream += weight * norm(value) (a layer norm, or with `centred` False a root-mean-square norm): `stream`
+    float32 or the dtype of value; summed in 32-bit.  `out` (dtype of value) receives the new stream, rounded:
+    what a part that reads the stream as it is multiplies with."""
+    _on_gpu(stream, value, weight, out)
+    assert stream.shape == value.shape and weight.dtype in (value.dtype, torch.float32)
+    assert stream.dtype in (torch.float32, value.dtype)
+    assert out is None or (out.shape == stream.shape and out.dtype == value.dtype)
+    flags = 1 | (0 if centred else 4) | (8 if out is not None else 0)
     _check(_fn("li_layernorm")(_code(value), stream.data_ptr(), _code(stream), value.data_ptr(), weight.data_ptr(),
-                               None, None, None, stream.shape[0], stream.shape[1], 0.0, float(eps), 1, _stream()),
-           "layernorm_add")
+                               None, _ptr(out), None, stream.shape[0], stream.shape[1], 0.0, float(eps), flags,
+                               _code(weight), _stream()), "layernorm_add")
     return stream
 
 
@@ -982,17 +1051,24 @@ def qk_projection_rmsnorm_(q: torch.Tensor, q_weight: torch.Tensor, k: torch.Ten
 
 
 def gated_rmsnorm(x: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
-                  heads: int) -> torch.Tensor:
-    """out[t, h] = weight * x[t, h] / sqrt(mean(x[t, h]^2) + eps) * silu(gate[t, h]) per head of `weight.numel()`
-    entries.  x and weight: float32, x [tokens, heads * size]; gate (a column slice is fine) and out in the engine's dtype."""
-    _on_gpu(x, weight, out)
+                  heads: int, gate_activation: str = "silu", den: torch.Tensor | None = None) -> torch.Tensor:
+    """out[t, h] = weight * x[t, h] / sqrt(mean(x[t, h]^2) + eps) * act(gate[t, h]) per head.  x: float32
+    [tokens, heads * size]; weight: float32, `size` entries shared by the heads or `heads * size`, one vector
+    per head; gate (a column slice is fine) and out in the engine's dtype.  `gate_activation`: "silu" or
+    "sigmoid".  `den` [tokens, heads] float32: x[t, h] is divided by den[t, h] first."""
+    _on_gpu(x, weight, out, den)
     _rows2d(gate, "gate")
     tokens, width = out.shape
-    size = weight.numel()
+    size = width // heads
     assert x.dtype == torch.float32 and x.shape == out.shape == gate.shape and width == heads * size
-    assert gate.dtype == out.dtype and weight.dtype == torch.float32
+    assert gate.dtype == out.dtype and weight.dtype == torch.float32 and weight.numel() in (size, width)
+    assert den is None or (den.dtype == torch.float32 and den.numel() == tokens * heads)
+    if gate_activation not in ("silu", "sigmoid"):
+        raise KernelLibraryError(f"gated_rmsnorm knows the gates 'silu' and 'sigmoid', not {gate_activation!r}")
     _check(_fn("li_gated_rmsnorm")(_code(out), x.data_ptr(), gate.data_ptr(), gate.stride(0), weight.data_ptr(),
-                                   out.data_ptr(), tokens, heads, size, float(eps), _stream()), "gated_rmsnorm")
+                                   out.data_ptr(), tokens, heads, size, float(eps),
+                                   int(weight.numel() == width and heads > 1), int(gate_activation == "sigmoid"),
+                                   _ptr(den), _stream()), "gated_rmsnorm")
     return out
 
 
@@ -1087,6 +1163,35 @@ def gated_delta_rule(qkv: torch.Tensor, ab: torch.Tensor, a_log: torch.Tensor, d
     if max_query_len != 1:
         global launch_count
         launch_count += 1   # two kernels
+    return out
+
+
+def mlstm(proj: torch.Tensor, offsets: tuple[int, int, int, int, int], i_bias: torch.Tensor, f_bias: torch.Tensor,
+          cap: float, state: torch.Tensor, maxima: torch.Tensor, query_start_loc: torch.Tensor,
+          state_slots: torch.Tensor, num_seqs: int, heads: int, dim: int, vdim: int, out: torch.Tensor,
+          den: torch.Tensor) -> torch.Tensor:
+    """The mLSTM matrix memory, token by token, on a 32-bit state per request and head.
+
+    proj [tokens, width] holds, per token, at the columns `offsets` = (q, k, v, i, f): q and k (heads of dim), v
+    (heads of vdim) and one raw input gate and one raw forget gate per head.  With x_i, x_f the raw gates plus
+    their biases (float32 [heads]):  i = cap tanh(x_i / cap);  f = logsigmoid(cap tanh(x_f / cap));
+    m' = max(f + m, i);  S <- exp(f + m - m') S + exp(i - m') k v^T;  n likewise with k alone;  m <- m'.
+    out [tokens, heads * vdim] float32 = S^T q dim^-0.5 (not yet divided), den [tokens, heads] float32 =
+    max(|n . q dim^-0.5|, exp(-m)) + 1e-6.  state [slots, heads, vdim + 1, dim] float32 (S column by column, n
+    as the last column) and maxima [slots, heads, vdim + 1] float32 (m, a copy per column) are read and written."""
+    _on_gpu(proj, i_bias, f_bias, state, maxima, query_start_loc, state_slots, out, den)
+    _int32(query_start_loc, "query_start_loc"); _int32(state_slots, "state_slots")
+    tokens, width = proj.shape
+    q_off, k_off, v_off, i_off, f_off = offsets
+    assert max(q_off, k_off) + heads * dim <= width and v_off + heads * vdim <= width and max(i_off, f_off) + heads <= width
+    assert i_bias.dtype == f_bias.dtype == state.dtype == maxima.dtype == out.dtype == den.dtype == torch.float32
+    assert i_bias.numel() == f_bias.numel() == heads
+    assert state.shape[1:] == (heads, vdim + 1, dim) and maxima.shape[1:] == (heads, vdim + 1)
+    assert out.shape == (tokens, heads * vdim) and den.shape == (tokens, heads)
+    _check(_fn("li_mlstm")(_code(proj), proj.data_ptr(), proj.stride(0), q_off, k_off, v_off, i_off, f_off,
+                           i_bias.data_ptr(), f_bias.data_ptr(), float(cap), state.data_ptr(), maxima.data_ptr(),
+                           query_start_loc.data_ptr(), state_slots.data_ptr(), tokens, num_seqs, out.data_ptr(),
+                           den.data_ptr(), heads, dim, vdim, _stream()), "mlstm")
     return out
 
 

@@ -33,19 +33,29 @@ class Attention:
     size than keys.  `softcap` > 0: a scaled score s becomes softcap * tanh(s / softcap).
     `qk_norm` "projection": q and k are each divided by their root mean square over the
     whole projection (all heads at once; eps `qk_norm_eps`) and multiplied by the weights
-    `q_norm.weight` / `k_norm.weight`, before the position encoding.  The three
-    projections are one product against the concatenated weights.
+    `q_norm.weight` / `k_norm.weight`, before the position encoding; "head": each head of q and of k is divided
+    by its own root mean square and multiplied by a weight of `head_dim` entries that the heads share.
+    `head_gate`: head h of the attention's output is multiplied by sigmoid(g_h), g = `g_proj.weight` x, one number
+    per head, before the output projection.  `value_mix`: "source" leaves this layer's values of the step's tokens
+    in `ctx.extras[value_mix_key]` for later layers; "mixed" stores (1 - l) v + l v_source instead of v, l the
+    scalar tensor `value_mix` and v_source what the source layer left for the same tokens.  Everything that reads
+    x is one product against the concatenated weights.
     """
 
     def __init__(self, hidden_size: int, heads: int, kv_heads: int, head_dim: int, position: PartSpec,
                  dtype: torch.dtype, device: torch.device, bias: bool = False, out_bias: bool | None = None,
                  window: int | None = None, scale: float | None = None, cache_name: str = "kv",
                  v_head_dim: int | None = None, keep_first: int = 0, softcap: float = 0.0,
-                 qk_norm: str | None = None, qk_norm_eps: float = 1e-6) -> None:
+                 qk_norm: str | None = None, qk_norm_eps: float = 1e-6, head_gate: bool = False,
+                 value_mix: str | None = None, value_mix_key: str = "value_mix") -> None:
         if heads % kv_heads:
             raise ValueError(f"heads={heads} is not a multiple of kv_heads={kv_heads}")
-        if qk_norm not in (None, "projection"):
-            raise ValueError(f"qk_norm {qk_norm!r} is not supported; known: None, 'projection'")
+        if qk_norm not in (None, "projection", "head"):
+            raise ValueError(f"qk_norm {qk_norm!r} is not supported; known: None, 'projection', 'head'")
+        if value_mix not in (None, "source", "mixed"):
+            raise ValueError(f"value_mix {value_mix!r} is not supported; known: None, 'source', 'mixed'")
+        self.head_gate, self.value_mix, self.value_mix_key = bool(head_gate), value_mix, value_mix_key
+        self.blend: torch.Tensor | None = None
         self.hidden_size, self.heads, self.kv_heads, self.head_dim = hidden_size, heads, kv_heads, head_dim
         self.v_head_dim = head_dim if v_head_dim is None else v_head_dim
         self.keep_first = int(keep_first) if window is not None else 0
@@ -72,9 +82,16 @@ class Attention:
             "v_proj.weight": TensorSpec((v, self.hidden_size)),
             "o_proj.weight": TensorSpec((self.hidden_size, self.heads * self.v_head_dim)),
         }
-        if self.qk_norm:
+        if self.qk_norm == "head":
+            specs.update({"q_norm.weight": TensorSpec((self.head_dim,), init="ones_normal"),
+                          "k_norm.weight": TensorSpec((self.head_dim,), init="ones_normal")})
+        elif self.qk_norm:
             specs.update({"q_norm.weight": TensorSpec((q,), init="ones_normal"),
                           "k_norm.weight": TensorSpec((kv,), init="ones_normal")})
+        if self.head_gate:
+            specs["g_proj.weight"] = TensorSpec((self.heads, self.hidden_size))
+        if self.value_mix == "mixed":
+            specs["value_mix"] = TensorSpec((), kind="f32", init=_blend_init)
         if self.bias:
             specs.update({"q_proj.bias": TensorSpec((q,), init="zeros"), "k_proj.bias": TensorSpec((kv,), init="zeros"),
                           "v_proj.bias": TensorSpec((v,), init="zeros")})
@@ -85,9 +102,20 @@ class Attention:
         return specs
 
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
-        self.qkv_weight = torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]])
+        weights = [tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]]
+        biases = [tensors[n] for n in ("q_proj.bias", "k_proj.bias", "v_proj.bias")] if self.bias else []
+        if self.head_gate:
+            # The gate's rows ride behind v, filled up to a multiple of 16 rows (what the products' tiles like).
+            gate = tensors["g_proj.weight"]
+            pad = -(sum(w.shape[0] for w in weights) + self.heads) % 16
+            weights += [gate, gate.new_zeros((pad, self.hidden_size))]
+            if self.bias:
+                biases.append(biases[0].new_zeros(self.heads + pad))
+        self.qkv_weight = torch.cat(weights).contiguous()
         if self.bias:
-            self.qkv_bias = torch.cat([tensors["q_proj.bias"], tensors["k_proj.bias"], tensors["v_proj.bias"]])
+            self.qkv_bias = torch.cat(biases).contiguous()
+        if self.value_mix == "mixed":
+            self.blend = tensors["value_mix"].to(torch.float32).reshape(1).contiguous()
         self.o_weight = tensors["o_proj.weight"]
         if self.qk_norm:
             self.q_norm_weight, self.k_norm_weight = tensors["q_norm.weight"], tensors["k_norm.weight"]
@@ -107,8 +135,10 @@ class Attention:
         tokens = x.shape[0]
         q_width, kv_width = self.heads * self.head_dim, self.kv_heads * self.head_dim
         v_width = self.kv_heads * self.v_head_dim
-        qkv = torch.empty((tokens, q_width + kv_width + v_width), dtype=x.dtype, device=x.device)
+        qkv = torch.empty((tokens, self.qkv_weight.shape[0]), dtype=x.dtype, device=x.device)
         ops.linear(x, self.qkv_weight, qkv, self.qkv_bias)
+        if self.qk_norm == "head" or self.head_gate or self.value_mix:
+            return self._forward_prepared(qkv, ctx, cache, residual)
         if self.qk_norm:
             ops.qk_projection_rmsnorm_(qkv[:, :q_width], self.q_norm_weight, qkv[:, q_width:q_width + kv_width],
                                        self.k_norm_weight, self.qk_norm_eps)
@@ -140,6 +170,54 @@ class Attention:
                             self.head_dim, self.scale, self.window or 0, plan=ctx.plan,
                             decode_splits=ctx.decode_splits, **masked)
         return ops.linear(attended, self.o_weight, None, self.o_bias, residual=residual)
+
+
+    def _forward_prepared(self, qkv: torch.Tensor, ctx: StepContext, cache: LayerCache, residual):
+        """The path of an attention with per-head q/k norms, mixed values or a head gate: one kernel normalises
+        and rotates q and k, blends v and stores k and v; the attention reads q from the projection's rows; the
+        gate multiplies the heads' outputs in place."""
+        kv = cache.kvs[self.cache_name]
+        tokens = qkv.shape[0]
+        q_width, kv_width = self.heads * self.head_dim, self.kv_heads * self.head_dim
+        v_width = self.kv_heads * self.v_head_dim
+        table = ctx.block_tables[kv.group]
+        rotary = self.position.rotary()
+        if rotary is None:
+            self.position.apply(qkv[:, :q_width].unflatten(1, (self.heads, self.head_dim)),
+                                qkv[:, q_width:q_width + kv_width].unflatten(1, (self.kv_heads, self.head_dim)), ctx)
+        elif rotary.attention_scaling != 1.0:
+            raise ValueError("this attention path rotates with plain cosines and sines (no stretch)")
+        values = qkv[:, q_width + kv_width:q_width + kv_width + v_width]
+        other = None
+        if self.value_mix == "source":
+            ctx.extras[self.value_mix_key] = values
+        elif self.value_mix == "mixed":
+            other = ctx.extras.get(self.value_mix_key)
+            if other is None or other.shape != values.shape:
+                raise ValueError("a layer that mixes values runs behind the layer whose values it mixes in, "
+                                 "with values of the same shape")
+        per_head = self.qk_norm == "head"
+        ops.head_norm_rope_kv_write(qkv, ctx.positions, ctx.seq_of_token, table, kv.k_pool, kv.v_pool,
+                                    rotary.inv_freq if rotary else None, self.heads, self.kv_heads, self.head_dim,
+                                    rotary.rotary_dim if rotary else 0,
+                                    self.q_norm_weight if per_head else None, self.k_norm_weight if per_head else None,
+                                    self.qk_norm_eps, store=not cache.read_only, v_other=other,
+                                    blend=self.blend if other is not None else None)
+        attended = torch.empty((tokens, self.heads * self.v_head_dim), dtype=qkv.dtype, device=qkv.device)
+        masked = dict(keep_first=self.keep_first, softcap=self.softcap) if (self.keep_first or self.softcap) else {}
+        ops.paged_attention(qkv, qkv.shape[1], attended, kv.k_pool, kv.v_pool, table, ctx.query_start_loc,
+                            ctx.context_lens, ctx.num_seqs, ctx.max_query_len, self.heads, self.kv_heads,
+                            self.head_dim, self.scale, self.window or 0, plan=ctx.plan,
+                            decode_splits=ctx.decode_splits, **masked)
+        if self.head_gate:
+            gate_at = q_width + kv_width + v_width
+            ops.sigmoid_gate_heads_(attended, qkv[:, gate_at:gate_at + self.heads], self.heads)
+        return ops.linear(attended, self.o_weight, None, self.o_bias, residual=residual)
+
+
+def _blend_init(shape, generator):
+    """A blending weight in [0.2, 0.8]."""
+    return 0.2 + 0.6 * torch.rand(shape, generator=generator)
 
 
 register_mixer("attention", Attention)

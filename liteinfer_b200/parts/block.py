@@ -102,6 +102,45 @@ class SandwichNormMixerBlock(SandwichNormBlock):
     roles = {"mixer_norm": "norm", "mixer": "mixer", "mixer_post_norm": "norm"}
 
 
+class OutputNormBlock:
+    """h = h + norm(mixer(h)); h = h + norm'(feed_forward(h)): the sublayers read the stream as it is, and only
+    what they give back is normalised.  The normalised output travels as an `ops.NormedDelta`; whoever reads the
+    stream next adds it: this block's `_read` (one kernel: the outgoing norm, the 32-bit sum, and the sum rounded
+    to the engine's dtype for the sublayer's products) or the model's final norm."""
+
+    roles = {"mixer": "mixer", "mixer_out_norm": "norm", "feed_forward": "feed_forward",
+             "feed_forward_out_norm": "norm"}
+
+    def __init__(self, parts: dict) -> None:
+        self.mixer, self.mixer_out_norm = parts["mixer"], parts["mixer_out_norm"]
+        self.feed_forward = parts.get("feed_forward")
+        self.feed_forward_out_norm = parts.get("feed_forward_out_norm")
+        self.dtype = self.mixer_out_norm.dtype
+
+    def _read(self, hidden: torch.Tensor, delta) -> torch.Tensor:
+        """Adds the pending delta into the stream and returns the stream in the engine's dtype."""
+        narrow = hidden.dtype != self.dtype
+        out = torch.empty(hidden.shape, dtype=self.dtype, device=hidden.device) if narrow else None
+        if isinstance(delta, ops.NormedDelta):
+            ops.layernorm_add(hidden, delta.value, delta.weight, delta.eps, centred=delta.centred, out=out)
+            return out if narrow else hidden
+        if isinstance(delta, torch.Tensor):
+            ops.add_(hidden, delta)
+        return ops.convert(hidden, out) if narrow else hidden
+
+    def forward(self, hidden: torch.Tensor, delta, ctx: StepContext, cache: LayerCache):
+        delta = self.mixer_out_norm.normed_delta(self.mixer.forward(self._read(hidden, delta), ctx, cache))
+        if self.feed_forward is None:
+            return hidden, delta
+        return hidden, self.feed_forward_out_norm.normed_delta(self.feed_forward.forward(self._read(hidden, delta), ctx))
+
+
+class OutputNormMixerBlock(OutputNormBlock):
+    """`OutputNormBlock` of a layer that has no feed-forward."""
+
+    roles = {"mixer": "mixer", "mixer_out_norm": "norm"}
+
+
 class StreamMixedBlock:
     """A pre-norm block whose residual is one or several 32-bit streams (parts/connection.py): every sublayer
     reads the streams through its connection's coefficients, and its output, scaled per channel, rewrites all
@@ -140,5 +179,7 @@ class StreamMixedMixerBlock(StreamMixedBlock):
 register_block("prenorm_residual", PreNormResidualBlock)
 register_block("stream_mixed", StreamMixedBlock)
 register_block("stream_mixed_mixer_only", StreamMixedMixerBlock)
+register_block("output_norm", OutputNormBlock)
+register_block("output_norm_mixer_only", OutputNormMixerBlock)
 register_block("sandwich_norm", SandwichNormBlock)
 register_block("sandwich_norm_mixer_only", SandwichNormMixerBlock)

@@ -18,6 +18,7 @@ import liteinfer_b200.parts.delta_rule  # noqa: F401
 import liteinfer_b200.parts.embedding  # noqa: F401
 import liteinfer_b200.parts.feed_forward  # noqa: F401
 import liteinfer_b200.parts.latent_attention  # noqa: F401
+import liteinfer_b200.parts.mlstm  # noqa: F401
 import liteinfer_b200.parts.norm  # noqa: F401
 import liteinfer_b200.parts.position  # noqa: F401
 import liteinfer_b200.parts.reentry  # noqa: F401
@@ -36,7 +37,7 @@ def _settled(hidden: torch.Tensor, delta, copies: int | None = None) -> torch.Te
             ops.stream_rmsnorm(out, None, 0.0, None, update=delta)
         return out.view(out.shape[0], copies, -1).sum(1)
     if isinstance(delta, ops.NormedDelta):
-        ops.layernorm_add(out, delta.value, delta.weight, delta.eps)
+        ops.layernorm_add(out, delta.value, delta.weight, delta.eps, centred=delta.centred)
     elif isinstance(delta, torch.Tensor):
         ops.add_(out, delta)
     return out

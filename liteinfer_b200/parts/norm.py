@@ -91,6 +91,43 @@ class LayerNorm:
         return ops.NormedDelta(value, self.weight, self.eps)
 
 
+def _around_zero(shape, generator):
+    return 0.05 * torch.randn(shape, generator=generator)
+
+
+class UnitOffsetRMSNorm:
+    """y = x / sqrt(mean(x^2) + eps) * (1 + weight): a root-mean-square norm whose stored weight lies around zero.
+
+    1 + weight is formed once, in 32-bit, when the tensors are bound.  Like `LayerNorm` it reads a stream that may
+    be 32-bit whatever the engine's dtype, writes the engine's dtype, and takes a pending `ops.NormedDelta`;
+    `normed_delta` makes one of a sublayer's output, for a block that normalises what a sublayer gives back."""
+
+    def __init__(self, size: int, eps: float, dtype: torch.dtype, device: torch.device) -> None:
+        self.size, self.eps, self.dtype, self.device = size, float(eps), dtype, device
+        self.weight: torch.Tensor | None = None         # 1 + the stored weight, float32
+
+    def tensor_specs(self) -> dict[str, TensorSpec]:
+        return {"weight": TensorSpec((self.size,), kind="f32", init=_around_zero)}
+
+    def bind(self, tensors: dict[str, torch.Tensor]) -> None:
+        self.weight = (1.0 + tensors["weight"].to(torch.float32)).contiguous()
+
+    def forward(self, x: torch.Tensor, delta: "torch.Tensor | ops.NormedDelta | None" = None,
+                rows: torch.Tensor | None = None, out: torch.Tensor | None = None):
+        if isinstance(delta, torch.Tensor):     # a plain delta: the sum first, then the norm
+            ops.add_(x, delta)
+            delta = None
+        n = x.shape[0] if rows is None else rows.numel()
+        if out is None:
+            out = torch.empty((n, self.size), dtype=self.dtype, device=x.device)
+        return ops.layernorm(x, self.weight, self.eps, out, delta=delta, rows=rows,
+                             write_stream=delta is not None and rows is None, centre=False)
+
+    def normed_delta(self, value: torch.Tensor) -> "ops.NormedDelta":
+        """What a sublayer's output becomes when this norm stands between it and the stream."""
+        return ops.NormedDelta(value, self.weight, self.eps, centred=False)
+
+
 class StreamRMSNorm:
     """y = u / sqrt(mean(u^2) + eps) * weight * out_scale, all in 32-bit, of a residual kept as `streams` 32-bit
     copies side by side in a row: u = sum_s read[s] * stream s (`read` None: the plain sum; with one stream, the
@@ -125,3 +162,4 @@ class StreamRMSNorm:
 register_norm("rmsnorm", RMSNorm)
 register_norm("stream_rmsnorm", StreamRMSNorm)
 register_norm("layernorm", LayerNorm)
+register_norm("rmsnorm_unit_offset", UnitOffsetRMSNorm)

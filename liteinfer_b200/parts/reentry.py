@@ -36,7 +36,7 @@ class EmbeddingRemix:
 
     def forward(self, hidden: torch.Tensor, delta, embedded: torch.Tensor):
         if isinstance(delta, ops.NormedDelta):
-            ops.layernorm_add(hidden, delta.value, delta.weight, delta.eps)
+            ops.layernorm_add(hidden, delta.value, delta.weight, delta.eps, centred=delta.centred)
         elif isinstance(delta, torch.Tensor):
             ops.add_(hidden, delta)
         h = self.hidden_size

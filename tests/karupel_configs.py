@@ -1,0 +1,72 @@
+"""Tiny Karupel configurations for the tests: they differ in every size, option and layer order.
+
+KAR_A: attention first; three value-mixing layers (the first one the source) with two key/value heads for four
+query heads and half-rotated heads with scaled frequencies; an mLSTM whose key size is no multiple of four; a delta
+layer with one q/k head for two value heads; feed-forwards on some layers only.
+KAR_B: starts with the delta layer; one attention that names value mixing alone (so nothing is mixed), without
+rotation; an mLSTM of one head; convolutions of one tap; values wider than keys.
+KAR_C: sizes that the tensor-core attention and the vector forms of the recurrences take (keys and values of 64),
+every dimension rotated without scaling, an attention without value mixing between two with it.
+"""
+
+import random
+
+KAR_A = {
+    "architecture": "Karupel", "vocab": 310, "width": 80, "norm": {"eps": 1e-5},
+    "layers": [
+        {"type": "attention", "mlp": {"kind": "dense", "ff": 96},
+         "mixer": {"heads": 4, "kv_heads": 2, "dim": 24, "vdim": 16, "scale": 0.21, "v_mix": True,
+                   "rot": {"dims": 12, "base": 10000.0, "scaling": {"factor": 4.0}}}},
+        {"type": "mlstm", "mlp": None, "mixer": {"heads": 3, "dim": 18, "vdim": 20, "gate_cap": 8.0}},
+        {"type": "attention", "mlp": None,
+         "mixer": {"heads": 2, "kv_heads": 2, "dim": 16, "vdim": 16, "scale": 0.3, "v_mix": True,
+                   "rot": {"dims": 16, "base": 500.0, "scaling": None}}},
+        {"type": "delta", "mlp": {"kind": "dense", "ff": 64},
+         "mixer": {"heads": 4, "kv_heads": 2, "dim": 24, "vdim": 12, "conv": 3}},
+        {"type": "attention", "mlp": {"kind": "dense", "ff": 48},
+         "mixer": {"heads": 6, "kv_heads": 2, "dim": 8, "vdim": 16, "scale": 0.4, "v_mix": True,
+                   "rot": {"dims": 4, "base": 100.0, "scaling": {"factor": 1.5}}}},
+    ],
+}
+
+KAR_B = {
+    "architecture": "Karupel", "vocab": 129, "width": 48, "norm": {"eps": 1e-6},
+    "layers": [
+        {"type": "delta", "mlp": None, "mixer": {"heads": 3, "kv_heads": 3, "dim": 8, "vdim": 24, "conv": 1}},
+        {"type": "mlstm", "mlp": {"kind": "dense", "ff": 72}, "mixer": {"heads": 1, "dim": 40, "vdim": 56, "gate_cap": 15.0}},
+        {"type": "attention", "mlp": {"kind": "dense", "ff": 40},
+         "mixer": {"heads": 3, "kv_heads": 1, "dim": 20, "vdim": 28, "scale": 0.25, "v_mix": True}},
+        {"type": "mlstm", "mlp": None, "mixer": {"heads": 5, "dim": 4, "vdim": 7, "gate_cap": 3.0}},
+    ],
+}
+
+KAR_C = {
+    "architecture": "Karupel", "vocab": 200, "width": 128, "norm": {"eps": 1e-5},
+    "layers": [
+        {"type": "mlstm", "mlp": None, "mixer": {"heads": 2, "dim": 64, "vdim": 32, "gate_cap": 10.0}},
+        {"type": "attention", "mlp": {"kind": "dense", "ff": 96},
+         "mixer": {"heads": 4, "kv_heads": 2, "dim": 64, "vdim": 64, "scale": 0.125, "v_mix": True,
+                   "rot": {"dims": 64, "base": 5000.0, "scaling": None}}},
+        {"type": "attention", "mlp": None,
+         "mixer": {"heads": 2, "kv_heads": 1, "dim": 64, "vdim": 64, "scale": 0.11,
+                   "rot": {"dims": 32, "base": 5000.0, "scaling": {"factor": 3.0}}}},
+        {"type": "delta", "mlp": None, "mixer": {"heads": 2, "kv_heads": 2, "dim": 64, "vdim": 32, "conv": 4}},
+        {"type": "attention", "mlp": {"kind": "dense", "ff": 96},
+         "mixer": {"heads": 4, "kv_heads": 2, "dim": 64, "vdim": 64, "scale": 0.125, "v_mix": True,
+                   "rot": {"dims": 64, "base": 5000.0, "scaling": None}}},
+    ],
+}
+
+# name -> (config, seed, page size)
+ALL = {"kar_a": (KAR_A, 21, 16), "kar_b": (KAR_B, 22, 4), "kar_c": (KAR_C, 23, 16)}
+
+
+def prompt(vocab: int, length: int, seed: int) -> list[int]:
+    rng = random.Random(seed)
+    return [rng.randrange(vocab) for _ in range(length)]
+
+
+# Largest absolute difference of float32 logits from the float64 plain implementation that rounding alone explains.
+FLOAT32_TOLERANCE = {"kar_a": 5e-5, "kar_b": 5e-5, "kar_c": 1e-4}
+# The same for bfloat16 (products' operands, pages and the sublayers' outputs are rounded; logits are of size 1).
+BFLOAT16_TOLERANCE = {"kar_a": 0.08, "kar_b": 0.08, "kar_c": 0.1}

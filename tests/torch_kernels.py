@@ -236,7 +236,7 @@ def layernorm(x, weight, eps, out, delta=None, rows=None, write_stream=False, ce
     v = (x if rows is None else x[rows.long()]).float()
     if delta is not None:
         d = (delta.value if rows is None else delta.value[rows.long()]).float()
-        v = v + delta.weight.float() * _norm(d, delta.eps)
+        v = v + delta.weight.float() * _norm(d, delta.eps, getattr(delta, "centred", True))
         if write_stream:
             x.copy_(v.to(x.dtype))
             v = x.float()
@@ -244,8 +244,10 @@ def layernorm(x, weight, eps, out, delta=None, rows=None, write_stream=False, ce
     return out
 
 
-def layernorm_add(stream, value, weight, eps):
-    stream.copy_((stream.float() + weight.float() * _norm(value.float(), eps)).to(stream.dtype))
+def layernorm_add(stream, value, weight, eps, centred=True, out=None):
+    stream.copy_((stream.float() + weight.float() * _norm(value.float(), eps, centred)).to(stream.dtype))
+    if out is not None:
+        out.copy_(stream.to(out.dtype))
     return stream
 
 
@@ -259,12 +261,79 @@ def qk_projection_rmsnorm_(q, q_weight, k, k_weight, eps):
     projection_rmsnorm_(k, k_weight, eps)
 
 
-def gated_rmsnorm(x, gate, weight, eps, out, heads):
+def gated_rmsnorm(x, gate, weight, eps, out, heads, gate_activation="silu", den=None):
     tokens, width = out.shape
     size = width // heads
     g = gate.float()
-    y = _norm(x.view(tokens, heads, size), eps, centre=False) * weight.float()
-    out.copy_((y.reshape(tokens, width) * (g / (1.0 + torch.exp(-g)))).to(out.dtype))
+    v = x.view(tokens, heads, size)
+    if den is not None:
+        v = v / den.view(tokens, heads, 1)
+    y = _norm(v, eps, centre=False) * weight.float().view(-1, size)
+    act = torch.sigmoid(g) if gate_activation == "sigmoid" else g / (1.0 + torch.exp(-g))
+    out.copy_((y.reshape(tokens, width) * act).to(out.dtype))
+    return out
+
+
+def head_norm_rope_kv_write(qkv, positions, seq_of_token, block_table, k_pool, v_pool, inv_freq, heads, kv_heads,
+                            head_dim, rotary_dim, q_norm, k_norm, norm_eps, store=True, v_other=None, blend=None):
+    """Per-head norms of q and k, the blend of v, then what `rope_kv_write` does, on a compact copy of the row."""
+    T, dtype = qkv.shape[0], qkv.dtype
+    vd = v_pool.shape[-1]
+    qw, kw, vw = heads * head_dim, kv_heads * head_dim, kv_heads * vd
+    q = qkv[:, :qw].float().view(T, heads, head_dim)
+    k = qkv[:, qw:qw + kw].float().view(T, kv_heads, head_dim)
+    v = qkv[:, qw + kw:qw + kw + vw].float()
+    if q_norm is not None:
+        q = _norm(q, norm_eps, centre=False) * q_norm.float()
+    if k_norm is not None:
+        k = _norm(k, norm_eps, centre=False) * k_norm.float()
+    if v_other is not None:
+        v = (1.0 - blend.float()) * v + blend.float() * v_other.float()
+    # The norm's result is not rounded before the rotation (the kernel rounds once); float32 rows carry it over.
+    compact = torch.cat([q.reshape(T, qw), k.reshape(T, kw), v], dim=1)
+    wide_k = torch.empty(k_pool.shape, dtype=torch.float32) if dtype != torch.float32 else k_pool
+    wide_v = torch.empty(v_pool.shape, dtype=torch.float32) if dtype != torch.float32 else v_pool
+    if dtype != torch.float32:
+        wide_k.copy_(k_pool); wide_v.copy_(v_pool)
+    rope_kv_write(compact, positions, seq_of_token, block_table, wide_k, wide_v, inv_freq, heads, kv_heads, head_dim,
+                  rotary_dim, store=store, v_head_dim=vd)
+    if dtype != torch.float32:
+        k_pool.copy_(wide_k); v_pool.copy_(wide_v)
+    qkv[:, :qw] = compact[:, :qw].to(dtype)
+
+
+def sigmoid_gate_heads_(x, gate, heads):
+    tokens, width = x.shape
+    y = x.float().view(tokens, heads, width // heads) * torch.sigmoid(gate.float())[:, :, None]
+    x.copy_(y.reshape(tokens, width).to(x.dtype))
+    return x
+
+
+def mlstm(proj, offsets, i_bias, f_bias, cap, state, maxima, query_start_loc, state_slots, num_seqs, heads, dim,
+          vdim, out, den):
+    """state: [slots, heads, vdim + 1, dim]: the transpose of S [dim, vdim] per head, then n; maxima: a copy of m
+    per column."""
+    qsl, slots = query_start_loc.tolist(), state_slots.tolist()
+    T = proj.shape[0]
+    q_off, k_off, v_off, i_off, f_off = offsets
+    q = proj[:, q_off:q_off + heads * dim].float().view(T, heads, dim) * dim ** -0.5
+    k = proj[:, k_off:k_off + heads * dim].float().view(T, heads, dim)
+    v = proj[:, v_off:v_off + heads * vdim].float().view(T, heads, vdim)
+    gi = cap * torch.tanh((proj[:, i_off:i_off + heads].float() + i_bias) / cap)
+    gf = torch.nn.functional.logsigmoid(cap * torch.tanh((proj[:, f_off:f_off + heads].float() + f_bias) / cap))
+    for s in range(num_seqs):
+        for t in range(qsl[s], qsl[s + 1]):
+            for h in range(heads):
+                cols = state[slots[s], h]                       # [vdim + 1, dim]
+                m = maxima[slots[s], h, 0]
+                m_new = torch.maximum(gf[t, h] + m, gi[t, h])
+                a, b = torch.exp(gf[t, h] + m - m_new), torch.exp(gi[t, h] - m_new)
+                values = torch.cat([v[t, h], torch.ones(1)])
+                cols.copy_(a * cols + b * values[:, None] * k[t, h][None, :])
+                maxima[slots[s], h] = m_new
+                read = cols @ q[t, h]
+                out[t, h * vdim:(h + 1) * vdim] = read[:vdim]
+                den[t, h] = torch.maximum(read[vdim].abs(), torch.exp(-m_new)) + 1e-6
     return out
 
 
@@ -499,7 +568,7 @@ def fused_decode_supports(*args) -> bool:
     return False      # the stand-ins rotate and store in `rope_kv_write`, never inside the attention
 
 
-ALL = ("embedding_streams", "stream_rmsnorm", "activation", "batched_linear", "latent_prep", "latent_attention",
+ALL = ("head_norm_rope_kv_write", "sigmoid_gate_heads_", "mlstm", "embedding_streams", "stream_rmsnorm", "activation", "batched_linear", "latent_prep", "latent_attention",
        "gate_heads", "convert", "layernorm", "layernorm_add", "projection_rmsnorm_", "qk_projection_rmsnorm_", "gated_rmsnorm",
        "short_conv", "short_conv_step", "short_conv_update", "gated_delta_rule", "fused_decode_supports", "scatter_tokens", "embedding", "rmsnorm", "add_", "add_bias_", "act_mul", "act_mul_interleaved", "gated_linear_supported",
        "gated_linear", "gemm_error_flag", "error_flags", "token_error_flag", "linear", "gemm_simt", "rope_kv_write", "paged_attention", "argmax", "sample")
