@@ -291,8 +291,8 @@ def head_norm_rope_kv_write(qkv, positions, seq_of_token, block_table, k_pool, v
         v = (1.0 - blend.float()) * v + blend.float() * v_other.float()
     # The norm's result is not rounded before the rotation (the kernel rounds once); float32 rows carry it over.
     compact = torch.cat([q.reshape(T, qw), k.reshape(T, kw), v], dim=1)
-    wide_k = torch.empty(k_pool.shape, dtype=torch.float32) if dtype != torch.float32 else k_pool
-    wide_v = torch.empty(v_pool.shape, dtype=torch.float32) if dtype != torch.float32 else v_pool
+    wide_k = torch.empty(k_pool.shape, dtype=torch.float32, device=k_pool.device) if dtype != torch.float32 else k_pool
+    wide_v = torch.empty(v_pool.shape, dtype=torch.float32, device=v_pool.device) if dtype != torch.float32 else v_pool
     if dtype != torch.float32:
         wide_k.copy_(k_pool); wide_v.copy_(v_pool)
     rope_kv_write(compact, positions, seq_of_token, block_table, wide_k, wide_v, inv_freq, heads, kv_heads, head_dim,
