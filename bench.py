@@ -15,6 +15,8 @@ decode at batch 1 and 64.  Weights are random (seeded) and token ids synthetic.
 `--compare kegizen` prints another line instead (the default run is unchanged): prefill and decode of the Kegizen
 decoder beside the Llama decoder at equal layer sizes, and the Kegizen kernels one by one beside their like.
 `--compare gifudra` does the same for the Gifudra decoder (latent attention, residual streams).
+`--compare karupel` sets the Karupel decoder (mLSTM, delta-rule and gated attention layers) beside a Kegizen decoder of
+the same sizes, its closest relative, and its kernels beside their like.
 """
 
 from __future__ import annotations
@@ -305,9 +307,11 @@ def run_ours(args) -> dict:
 
 
 # ---- `--compare kegizen`: the Kegizen decoder beside the Llama decoder at equal layer sizes ----------------------
-def _kegizen_config(width: int, ff: int, layers: int, heads: int, kv_heads: int, head_dim: int, vocab: int) -> dict:
+def _kegizen_config(width: int, ff: int, layers: int, heads: int, kv_heads: int, head_dim: int, vocab: int,
+                    plain_attention: bool = False) -> dict:
     """Three delta-rule layers, then one attention layer (a window of 1,024 that keeps 4 tokens, capped scores,
-    YaRN-scaled rotation of all of the head), over and over; every projection as wide as the Llama layer's."""
+    YaRN-scaled rotation of all of the head), over and over; every projection as wide as the Llama layer's.
+    `plain_attention`: causal attention over everything, uncapped, unscaled rotation."""
     delta = {"type": "delta", "mlp": {"kind": "dense", "ff": ff},
              "mixer": {"heads": heads * head_dim // 128, "kv_heads": heads * head_dim // 128, "dim": 128, "vdim": 128, "conv": 4}}
     attention = {"type": "attention", "mlp": {"kind": "dense", "ff": ff},
@@ -315,8 +319,28 @@ def _kegizen_config(width: int, ff: int, layers: int, heads: int, kv_heads: int,
                            "scale": head_dim ** -0.5, "softcap": 30.0, "mask": {"size": 1024, "keep_first": 4},
                            "rot": {"dims": head_dim, "base": 10000.0,
                                    "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    if plain_attention:
+        attention["mixer"] = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim,
+                              "scale": head_dim ** -0.5, "rot": {"dims": head_dim, "base": 10000.0, "scaling": None}}
     return {"architecture": "Kegizen", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
             "layers": [attention if i % 4 == 3 else delta for i in range(layers)], "loop": None}
+
+
+def _karupel_config(width: int, ff: int, layers: int, heads: int, kv_heads: int, head_dim: int, vocab: int) -> dict:
+    """mLSTM, delta rule, mLSTM, attention, over and over: the recurrent layers with heads of 128 x 128 as wide as the
+    model, the attention with the Llama layer's heads (half of each head rotated, scaled frequencies, per-head q/k
+    norms, the head gate, values mixed with the first attention's); a feed-forward in every layer."""
+    wide = heads * head_dim // 128
+    mlp = {"kind": "dense", "ff": ff}
+    mlstm = {"type": "mlstm", "mlp": mlp, "mixer": {"heads": wide, "dim": 128, "vdim": 128, "gate_cap": 15.0}}
+    delta = {"type": "delta", "mlp": mlp, "mixer": {"heads": wide, "kv_heads": wide, "dim": 128, "vdim": 128, "conv": 4}}
+    attention = {"type": "attention", "mlp": mlp,
+                 "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim,
+                           "scale": head_dim ** -0.5, "v_mix": True,
+                           "rot": {"dims": head_dim // 2, "base": 10000.0, "scaling": {"factor": 2.0}}}}
+    order = (mlstm, delta, mlstm, attention)
+    return {"architecture": "Karupel", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "layers": [order[i % 4] for i in range(layers)]}
 
 
 def _timed(fn, repeats: int = 20, warmup: int = 5, inner: int = 1) -> float:
@@ -541,6 +565,99 @@ def _gifudra_kernels(peaks: dict) -> dict:
     return {k: round(v, 4) for k, v in out.items()}
 
 
+def _karupel_kernels(peaks: dict) -> dict:
+    """Each kernel that the Karupel design brought, alone beside the like kernel of the Kegizen path, as fractions of
+    the measured copy bandwidth; inputs larger than L2, so every call reads from memory."""
+    import torch
+
+    from liteinfer_b200 import ops
+
+    dev, bf = "cuda:0", torch.bfloat16
+    hbm = peaks["hbm_gbs"] * 1e9
+    out: dict = {}
+
+    def ints(v):
+        return torch.tensor(v, dtype=torch.int32, device=dev)
+
+    def in_graph(fn, inner: int = 10) -> float:
+        fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(inner):
+                fn()
+        return _timed(graph.replay, repeats=10, warmup=2) / inner
+
+    # -- the norm on a sublayer's way out: stream (32-bit) += (1 + w) * value / rms(value), and the sum rounded
+    T, W = 16384, 2048
+    x32, value = torch.randn(T, W, device=dev), torch.randn(T, W, device=dev).to(bf)
+    w32, w16 = torch.ones(W, device=dev), torch.ones(W, dtype=bf, device=dev)
+    rounded = torch.empty(T, W, dtype=bf, device=dev)
+    ms = _timed(lambda: ops.layernorm_add(x32, value, w32, 1e-5, centred=False, out=rounded))
+    out["output_norm_hbm_frac"] = T * W * (4 + 2 + 4 + 2) / (ms * 1e-3) / hbm
+    ms = _timed(lambda: ops.layernorm(x32, w16, 1e-5, rounded, delta=ops.NormedDelta(value, w16, 1e-5), write_stream=True))
+    out["kegizen_layernorm_fused_hbm_frac"] = T * W * (4 + 2 + 4 + 2) / (ms * 1e-3) / hbm
+
+    # -- the gated norm behind a recurrence: the mLSTM's (divisor, sigmoid gate, weights per head) and the delta rule's
+    H, d = 16, 128
+    read, gate = torch.randn(T, H * d, device=dev), torch.randn(T, H * d, device=dev).to(bf)
+    den, gated = torch.rand(T, H, device=dev) + 0.5, torch.empty(T, H * d, dtype=bf, device=dev)
+    wide_w, head_w = torch.ones(H * d, device=dev), torch.ones(d, device=dev)
+    ms = _timed(lambda: ops.gated_rmsnorm(read, gate, wide_w, 1e-5, gated, H, gate_activation="sigmoid", den=den))
+    out["mlstm_gated_norm_hbm_frac"] = T * H * d * (4 + 2 + 2) / (ms * 1e-3) / hbm
+    ms = _timed(lambda: ops.gated_rmsnorm(read, gate, head_w, 1e-5, gated, H))
+    out["kegizen_gated_norm_hbm_frac"] = T * H * d * (4 + 2 + 2) / (ms * 1e-3) / hbm
+
+    # -- the recurrences: single tokens of 64 and 8 requests (16 heads of 128 x 128: 134 MB of state read and written
+    #    at 64) and a prompt of 2,048
+    for batch, tokens_each, key in ((64, 1, "decode_b64"), (8, 1, "decode_b8"), (1, 2048, "prompt_2048")):
+        n = batch * tokens_each
+        q2, sl = ints([i * tokens_each for i in range(batch + 1)]), ints(list(range(batch)))
+        proj = torch.randn(n, 4 * H * d + 2 * H, device=dev).to(bf)
+        state, maxima = torch.zeros(batch, H, d + 1, d, device=dev), torch.zeros(batch, H, d + 1, device=dev)
+        o, dn = torch.empty(n, H * d, device=dev), torch.empty(n, H, device=dev)
+        bias = torch.zeros(H, device=dev)
+        offsets = (0, H * d, 2 * H * d, 4 * H * d, 4 * H * d + H)
+        run_m = lambda: ops.mlstm(proj, offsets, bias, bias, 15.0, state, maxima, q2, sl, batch, H, d, d, o, dn)  # noqa: E731
+        qkv, ab = torch.randn(n, 3 * H * d, device=dev).to(bf), torch.randn(n, 2 * H, device=dev).to(bf)
+        s2 = torch.zeros(batch, H, d, d, device=dev)
+        run_d = lambda: ops.gated_delta_rule(qkv, ab, bias, bias, s2, q2, sl, batch, H, H, d, d, o, tokens_each)  # noqa: E731
+        for name, run, rows in (("mlstm", run_m, d + 1), ("kegizen_delta_rule", run_d, d)):
+            ms = in_graph(run) if tokens_each == 1 else _timed(run)
+            out[f"{name}_{key}_us"] = ms * 1e3
+            if tokens_each == 1:
+                out[f"{name}_{key}_hbm_frac"] = batch * H * rows * d * 4 * 2 / (ms * 1e-3) / hbm
+            else:
+                out[f"{name}_{key}_us_per_token"] = ms * 1e3 / tokens_each
+
+    # -- what stands in front of the attention: per-head norms, rotation, blend of the values, pages; beside the
+    #    plain rotation and store.  16,384 tokens of 32 / 8 heads of 128.
+    heads, kv_heads, hd, page = 32, 8, 128, 16
+    pages = T // page
+    row = (heads + 2 * kv_heads) * hd
+    qkv = torch.randn(T, row + 32, device=dev).to(bf)
+    other = torch.randn(T, kv_heads * hd, device=dev).to(bf)
+    k_pool, v_pool = (torch.empty(pages, kv_heads, page, hd, dtype=bf, device=dev) for _ in range(2))
+    table = torch.arange(pages, dtype=torch.int32, device=dev).view(1, pages)
+    positions, seq_of = torch.arange(T, dtype=torch.int32, device=dev), torch.zeros(T, dtype=torch.int32, device=dev)
+    inv_half = (10000.0 ** (-torch.arange(0, hd // 2, 2, dtype=torch.float32) / (hd // 2)) / 2.0).to(dev)
+    inv_full = (10000.0 ** (-torch.arange(0, hd, 2, dtype=torch.float32) / hd)).to(dev)
+    norm_w, blend = torch.ones(hd, dtype=bf, device=dev), torch.tensor([0.4], device=dev)
+    ms = _timed(lambda: ops.head_norm_rope_kv_write(qkv, positions, seq_of, table, k_pool, v_pool, inv_half, heads,
+                                                    kv_heads, hd, hd // 2, norm_w, norm_w, 1e-5, v_other=other, blend=blend))
+    moved = T * hd * 2 * (2 * heads + 2 * kv_heads + 3 * kv_heads)      # q read and written; k, v read and stored; the other v
+    out["head_norm_rope_store_hbm_frac"] = moved / (ms * 1e-3) / hbm
+    exact = qkv[:, :row].contiguous()
+    ms = _timed(lambda: ops.rope_kv_write(exact, positions, seq_of, table, k_pool, v_pool, inv_full, heads, kv_heads, hd, hd))
+    out["kegizen_rope_store_hbm_frac"] = T * hd * 2 * (2 * heads + 4 * kv_heads) / (ms * 1e-3) / hbm
+
+    # -- the gate on the heads' outputs (in place)
+    attended, gates = torch.randn(T, heads * hd, device=dev).to(bf), torch.randn(T, heads, device=dev).to(bf)
+    ms = _timed(lambda: ops.sigmoid_gate_heads_(attended, gates, heads))
+    out["head_gate_hbm_frac"] = T * heads * hd * 2 * 2 / (ms * 1e-3) / hbm
+    return {k: round(v, 4) for k, v in out.items()}
+
+
 def run_kegizen(args, which: str = "kegizen") -> dict:
     """Prefill (one prompt of 2,048 tokens) and decode (batch 8 and 64 near a context of 2,048) of a Kegizen (or
     Gifudra) model and of a Llama model with the same width, depth, head sizes and feed-forward, random weights,
@@ -561,14 +678,17 @@ def run_kegizen(args, which: str = "kegizen") -> dict:
     if which == "gifudra":      # heads of 128 in both sizes: the latent attention's heads are 128 + 64 wide
         sizes = {"w2048": dict(width=2048, ff=8192, layers=8, heads=16, kv_heads=4, head_dim=128),
                  "w4096": dict(width=4096, ff=14336, layers=4, heads=32, kv_heads=8, head_dim=128)}
-    design = _gifudra_config if which == "gifudra" else _kegizen_config
+    design = {"gifudra": _gifudra_config, "karupel": _karupel_config}.get(which, _kegizen_config)
     result: dict = {"impl": "ours", "compare": which, "dtype": "bf16", "data": "synthetic ids, random weights",
                     "peaks": peaks, "models": {}}
     for name, size in sizes.items():
         llama = dict(LLAMA_1B, vocab_size=vocab, hidden_size=size["width"], intermediate_size=size["ff"],
                      num_hidden_layers=size["layers"], num_attention_heads=size["heads"],
                      num_key_value_heads=size["kv_heads"], head_dim=size["head_dim"], tie_word_embeddings=False)
-        for arch, cfg in ((which, design(vocab=vocab, **size)), ("llama", llama)):
+        beside = ("llama", llama)
+        if which == "karupel":      # its closest relative: delta-rule layers and plain causal attention, the same sizes
+            beside = ("kegizen", _kegizen_config(vocab=vocab, plain_attention=True, **size))
+        for arch, cfg in ((which, design(vocab=vocab, **size)), beside):
             with tempfile.TemporaryDirectory() as tmp:
                 model_dir = write_random_model(cfg, Path(tmp) / arch, seed=0)
                 llm = LLM(str(model_dir), dtype="bfloat16", device="cuda:0", max_num_seqs=64, max_model_len=context + 1,
@@ -595,7 +715,8 @@ def run_kegizen(args, which: str = "kegizen") -> dict:
                 runner.check_kernels()
                 llm.close()
                 result["models"][f"{name}_{arch}"] = numbers
-    result["kernels"] = _gifudra_kernels(peaks) if which == "gifudra" else _kegizen_kernels(peaks)
+    kernels = {"gifudra": _gifudra_kernels, "karupel": _karupel_kernels}.get(which, _kegizen_kernels)
+    result["kernels"] = kernels(peaks)
     return result
 
 
@@ -736,9 +857,10 @@ def main() -> int:
     parser.add_argument("--workload", default="none", choices=["none", "3b", "8b", "all"],
                         help="run the reference's larger configurations instead (64 requests under continuous batching "
                              "at the 3B sizes; decode at a context of 8,192 at the 8B sizes) and print their line")
-    parser.add_argument("--compare", default="none", choices=["none", "kegizen", "gifudra"],
-                        help="instead of the default run: the Kegizen (or Gifudra) decoder beside the Llama decoder at "
-                             "equal layer sizes (prefill, decode, and the design's kernels one by one)")
+    parser.add_argument("--compare", default="none", choices=["none", "kegizen", "gifudra", "karupel"],
+                        help="instead of the default run: the Kegizen (or Gifudra) decoder beside the Llama decoder, or "
+                             "the Karupel decoder beside the Kegizen decoder, at equal layer sizes (prefill, decode, and "
+                             "the design's kernels one by one)")
     parser.add_argument("--no-workloads", action="store_true",
                         help="leave the 3B and 8B configurations out of the default run (they add about 80 s)")
     args = parser.parse_args()
