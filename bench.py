@@ -618,7 +618,8 @@ def _karupel_kernels(peaks: dict) -> dict:
         o, dn = torch.empty(n, H * d, device=dev), torch.empty(n, H, device=dev)
         bias = torch.zeros(H, device=dev)
         offsets = (0, H * d, 2 * H * d, 4 * H * d, 4 * H * d + H)
-        run_m = lambda: ops.mlstm(proj, offsets, bias, bias, 15.0, state, maxima, q2, sl, batch, H, d, d, o, dn)  # noqa: E731
+        run_m = lambda: ops.mlstm(proj, offsets, bias, bias, 15.0, state, maxima, q2, sl, batch, H, d, d, o, dn,  # noqa: E731
+                                  tokens_each)
         qkv, ab = torch.randn(n, 3 * H * d, device=dev).to(bf), torch.randn(n, 2 * H, device=dev).to(bf)
         s2 = torch.zeros(batch, H, d, d, device=dev)
         run_d = lambda: ops.gated_delta_rule(qkv, ab, bias, bias, s2, q2, sl, batch, H, H, d, d, o, tokens_each)  # noqa: E731

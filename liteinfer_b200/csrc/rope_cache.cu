@@ -102,6 +102,120 @@ head_norm_rope_kv_write_kernel(T* __restrict__ qkv, size_t row_stride, const int
   }
 }
 
+// The same, a 16-byte vector of neighbouring dimensions a thread: `group` = head_dim / N threads share a head (a power
+// of two up to 32, so a head never straddles warps), add up its squares with shuffles, and fetch the rotation's
+// partner vector (half a rotary width away: a whole number of vectors) from the lane that holds it.  All items of
+// a token are independent loads, so many are in flight at once.
+template <typename T>
+__global__ void __launch_bounds__(kPrepWarps * 32)
+head_norm_rope_kv_write_vec_kernel(T* __restrict__ qkv, size_t row_stride, const int* __restrict__ positions,
+                                   const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
+                                   int table_stride, T* __restrict__ k_pool, T* __restrict__ v_pool,
+                                   const float* __restrict__ inv_freq, int heads, int kv_heads, int head_dim,
+                                   int rotary_dim, int page_size, int num_pages, int v_dim,
+                                   const T* __restrict__ q_norm, const T* __restrict__ k_norm, float norm_eps,
+                                   const T* __restrict__ v_other, size_t v_other_stride,
+                                   const float* __restrict__ lambda, int group_shift) {
+  constexpr int N = Vec16<T>::N;
+  extern __shared__ float shared[];  // cos[half], sin[half]
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31;
+  grid_launch_dependents();
+  const int pos = positions[t];
+  const int half = rotary_dim / 2;
+  float* cosv = shared;
+  float* sinv = shared + half;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    const float angle = __fmul_rn((float)pos, inv_freq[i]);
+    cosv[i] = cosf(angle);
+    sinv[i] = sinf(angle);
+  }
+  const int seq = seq_of_token[t];
+  const int page = seq < 0 ? -1 : block_table[(size_t)seq * table_stride + pos / page_size];
+  const bool store = page >= 0 && page < num_pages;
+  const int slot = pos % page_size;
+  const float mix = lambda != nullptr ? lambda[0] : 0.f;
+  grid_dependency_wait();           // q, k and v come from the projection before this kernel
+  __syncthreads();
+
+  T* row = qkv + (size_t)t * row_stride;
+  const int group = 1 << group_shift;
+  const int qk_items = (heads + kv_heads) << group_shift;
+  const int apart = half / N;       // lanes between the two vectors of a rotated pair
+  for (int base = 0; base < qk_items; base += kPrepWarps * 32) {
+    const int item = base + threadIdx.x;
+    const bool active = item < qk_items;         // a head's lanes are active together
+    const int h = active ? item >> group_shift : 0, j0 = (item & (group - 1)) * N;
+    const bool is_q = h < heads;
+    T* p = row + (size_t)h * head_dim + j0;
+    float x[N];
+#pragma unroll
+    for (int e = 0; e < N; ++e) x[e] = 0.f;
+    if (active) unpack16(load16(p), x);
+    const T* w = is_q ? q_norm : k_norm;
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < N; ++e) ss = fmaf(x[e], x[e], ss);
+    for (int o = group >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);   // by every lane of the warp
+    if (w != nullptr) {
+      const float inv = 1.0f / sqrtf(ss / (float)head_dim + norm_eps);
+      float wv[N];
+      unpack16(load16(w + j0), wv);
+#pragma unroll
+      for (int e = 0; e < N; ++e) x[e] = x[e] * inv * wv[e];
+    }
+    const int from = j0 < half ? lane + apart : (j0 < rotary_dim ? lane - apart : lane);
+    Vec16<T> result;
+#pragma unroll
+    for (int e = 0; e < N; ++e) {
+      const float y = __shfl_sync(0xffffffffu, x[e], from);
+      float r = x[e];
+      if (j0 < half) r = rotate_lo(x[e], y, cosv[j0 + e], sinv[j0 + e]);
+      else if (j0 < rotary_dim) r = rotate_hi(y, x[e], cosv[j0 - half + e], sinv[j0 - half + e]);
+      result.set(e, r);
+    }
+    if (active && (is_q || store)) {
+      T* dst = is_q ? p : k_pool + (((size_t)page * kv_heads + (h - heads)) * page_size + slot) * head_dim + j0;
+      store16(dst, result);
+    }
+  }
+  if (!store) return;
+  const T* vrow = row + (size_t)(heads + kv_heads) * head_dim;
+  const T* orow = v_other != nullptr ? v_other + (size_t)t * v_other_stride : nullptr;
+  for (int w = threadIdx.x * N; w < kv_heads * v_dim; w += kPrepWarps * 32 * N) {
+    const int h = w / v_dim, j = w - h * v_dim;
+    Vec16<T> v = load16(vrow + w);
+    if (orow != nullptr) {
+      float a[N], b[N];
+      unpack16(v, a);
+      unpack16(load16(orow + w), b);
+#pragma unroll
+      for (int e = 0; e < N; ++e) v.set(e, fmaf(mix, b[e], (1.0f - mix) * a[e]));
+    }
+    store16(v_pool + (((size_t)page * kv_heads + h) * page_size + slot) * v_dim + j, v);
+  }
+}
+
+// x [tokens, heads * size] in 16-byte vectors (size a multiple of the vector's length).
+template <typename T>
+__global__ void sigmoid_gate_heads_vec_kernel(T* __restrict__ x, const T* __restrict__ gate, size_t gate_stride,
+                                              size_t tokens, int heads, int size) {
+  constexpr int N = Vec16<T>::N;
+  grid_dependency_wait();
+  const size_t width = (size_t)heads * size / N, total = tokens * width;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / width;
+    const int h = (int)((i - t * width) * N / size);
+    const float g = 1.0f / (1.0f + expf(-to_float(gate[t * gate_stride + h])));
+    Vec16<T> v = load16(x + i * N);
+    float a[N];
+    unpack16(v, a);
+#pragma unroll
+    for (int e = 0; e < N; ++e) v.set(e, a[e] * g);
+    store16(x + i * N, v);
+  }
+}
+
 template <typename T>
 __global__ void sigmoid_gate_heads_kernel(T* __restrict__ x, const T* __restrict__ gate, size_t gate_stride,
                                           size_t tokens, int heads, int size) {
@@ -277,6 +391,33 @@ LI_EXPORT int li_head_norm_rope_kv_write(int dtype, void* qkv, size_t row_stride
   if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return LI_ERR_UNSUPPORTED;
   if (rotary_dim > 0 && inv_freq == nullptr) return LI_ERR_UNSUPPORTED;
   if ((v_other == nullptr) != (lambda == nullptr)) return LI_ERR_UNSUPPORTED;
+  {
+    // Vectors of 16 bytes where each lies within one head and one side of the rotation, a head's vectors fit in a
+    // warp, and every pointer and stride is a multiple of 16 bytes.
+    const int n = dtype == kFloat32 ? 4 : 8;
+    const int group = head_dim / n;
+    const bool pow2 = head_dim % n == 0 && group >= 1 && group <= 32 && (group & (group - 1)) == 0;
+    const bool fits = pow2 && (rotary_dim / 2) % n == 0 && v_dim % n == 0 && row_stride % n == 0 &&
+                      (v_other == nullptr || v_other_stride % n == 0) && aligned16(qkv) && aligned16(k_pool) &&
+                      aligned16(v_pool) && aligned16(q_norm) && aligned16(k_norm) && aligned16(v_other) &&
+                      (size_t)rotary_dim * sizeof(float) <= 48 * 1024;
+    if (fits) {
+      int shift = 0;
+      while ((1 << shift) < group) ++shift;
+      const size_t cs = (size_t)rotary_dim * sizeof(float);
+      if (dtype == kFloat32)
+        return (int)launch_pdl(tokens, head_norm_rope_kv_write_vec_kernel<float>, dim3(tokens), dim3(kPrepWarps * 32), cs,
+                               stream, (float*)qkv, row_stride, positions, seq_of_token, block_table, table_stride,
+                               (float*)k_pool, (float*)v_pool, inv_freq, heads, kv_heads, head_dim, rotary_dim,
+                               page_size, num_pages, v_dim, (const float*)q_norm, (const float*)k_norm, norm_eps,
+                               (const float*)v_other, v_other_stride, lambda, shift);
+      return (int)launch_pdl(tokens, head_norm_rope_kv_write_vec_kernel<bf16>, dim3(tokens), dim3(kPrepWarps * 32), cs,
+                             stream, (bf16*)qkv, row_stride, positions, seq_of_token, block_table, table_stride,
+                             (bf16*)k_pool, (bf16*)v_pool, inv_freq, heads, kv_heads, head_dim, rotary_dim, page_size,
+                             num_pages, v_dim, (const bf16*)q_norm, (const bf16*)k_norm, norm_eps,
+                             (const bf16*)v_other, v_other_stride, lambda, shift);
+    }
+  }
   const size_t smem = ((size_t)rotary_dim + (size_t)kPrepWarps * head_dim) * sizeof(float);
   if (smem > 48 * 1024) return LI_ERR_UNSUPPORTED;
   if (dtype == kFloat32)
@@ -296,6 +437,16 @@ LI_EXPORT int li_sigmoid_gate_heads(int dtype, void* x, const void* gate, size_t
                                     int size, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (heads < 1 || size < 1) return LI_ERR_UNSUPPORTED;
+  const int n = dtype == kFloat32 ? 4 : 8;
+  if (size % n == 0 && aligned16(x)) {
+    const size_t vectors = (size_t)tokens * heads * size / n;
+    const dim3 vgrid((unsigned)((vectors + 255) / 256 < 8192 ? (vectors + 255) / 256 : 8192));
+    if (dtype == kFloat32)
+      return (int)launch_pdl(tokens, sigmoid_gate_heads_vec_kernel<float>, vgrid, dim3(256), 0, stream, (float*)x,
+                             (const float*)gate, gate_stride, (size_t)tokens, heads, size);
+    return (int)launch_pdl(tokens, sigmoid_gate_heads_vec_kernel<bf16>, vgrid, dim3(256), 0, stream, (bf16*)x,
+                           (const bf16*)gate, gate_stride, (size_t)tokens, heads, size);
+  }
   const size_t total = (size_t)tokens * heads * size;
   const dim3 grid((unsigned)((total + 255) / 256 < 8192 ? (total + 255) / 256 : 8192));
   if (dtype == kFloat32)

@@ -54,7 +54,7 @@ _SIGNATURES = {
     "li_sigmoid_gate_heads": ("rope_cache", [c_int, c_void_p, c_void_p, c_size_t, c_int, c_int, c_int, c_void_p]),
     "li_mlstm": ("mlstm", [c_int, c_void_p, c_size_t, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
                            c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
-                           c_int, c_void_p]),
+                           c_int, c_int, c_void_p]),
     "li_paged_attention_generic": ("attention_generic", [
         c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_float, c_void_p]),
@@ -1169,7 +1169,7 @@ def gated_delta_rule(qkv: torch.Tensor, ab: torch.Tensor, a_log: torch.Tensor, d
 def mlstm(proj: torch.Tensor, offsets: tuple[int, int, int, int, int], i_bias: torch.Tensor, f_bias: torch.Tensor,
           cap: float, state: torch.Tensor, maxima: torch.Tensor, query_start_loc: torch.Tensor,
           state_slots: torch.Tensor, num_seqs: int, heads: int, dim: int, vdim: int, out: torch.Tensor,
-          den: torch.Tensor) -> torch.Tensor:
+          den: torch.Tensor, max_query_len: int = 0) -> torch.Tensor:
     """The mLSTM matrix memory, token by token, on a 32-bit state per request and head.
 
     proj [tokens, width] holds, per token, at the columns `offsets` = (q, k, v, i, f): q and k (heads of dim), v
@@ -1178,7 +1178,8 @@ def mlstm(proj: torch.Tensor, offsets: tuple[int, int, int, int, int], i_bias: t
     m' = max(f + m, i);  S <- exp(f + m - m') S + exp(i - m') k v^T;  n likewise with k alone;  m <- m'.
     out [tokens, heads * vdim] float32 = S^T q dim^-0.5 (not yet divided), den [tokens, heads] float32 =
     max(|n . q dim^-0.5|, exp(-m)) + 1e-6.  state [slots, heads, vdim + 1, dim] float32 (S column by column, n
-    as the last column) and maxima [slots, heads, vdim + 1] float32 (m, a copy per column) are read and written."""
+    as the last column) and maxima [slots, heads, vdim + 1] float32 (m, a copy per column) are read and written.
+    `max_query_len`: the most tokens a sequence brings, if known (the kernel then stages no more than that)."""
     _on_gpu(proj, i_bias, f_bias, state, maxima, query_start_loc, state_slots, out, den)
     _int32(query_start_loc, "query_start_loc"); _int32(state_slots, "state_slots")
     tokens, width = proj.shape
@@ -1191,7 +1192,7 @@ def mlstm(proj: torch.Tensor, offsets: tuple[int, int, int, int, int], i_bias: t
     _check(_fn("li_mlstm")(_code(proj), proj.data_ptr(), proj.stride(0), q_off, k_off, v_off, i_off, f_off,
                            i_bias.data_ptr(), f_bias.data_ptr(), float(cap), state.data_ptr(), maxima.data_ptr(),
                            query_start_loc.data_ptr(), state_slots.data_ptr(), tokens, num_seqs, out.data_ptr(),
-                           den.data_ptr(), heads, dim, vdim, _stream()), "mlstm")
+                           den.data_ptr(), heads, dim, vdim, int(max_query_len), _stream()), "mlstm")
     return out
 
 

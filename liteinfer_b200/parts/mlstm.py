@@ -84,7 +84,8 @@ class MLSTM:
         read = torch.empty((tokens, self.v_width), dtype=torch.float32, device=x.device)
         den = torch.empty((tokens, self.heads), dtype=torch.float32, device=x.device)
         ops.mlstm(proj, (0, self.k_at, self.v_at, self.i_at, self.f_at), self.i_bias, self.f_bias, self.gate_cap, state,
-                  maxima, ctx.query_start_loc, ctx.state_slots, ctx.num_seqs, self.heads, self.dim, self.vdim, read, den)
+                  maxima, ctx.query_start_loc, ctx.state_slots, ctx.num_seqs, self.heads, self.dim, self.vdim, read, den,
+                  ctx.max_query_len)
         gated = torch.empty((tokens, self.v_width), dtype=x.dtype, device=x.device)
         ops.gated_rmsnorm(read, proj[:, self.g_at:self.g_at + self.v_width], self.norm_weight, self.norm_eps, gated,
                           self.heads, gate_activation="sigmoid", den=den)

@@ -56,8 +56,10 @@ def _run_mlstm(impl, proj, lengths, cuts, slots, heads, dim, vdim, cap, i_bias, 
             qsl.append(qsl[-1] + c)
         out = torch.zeros(rows.shape[0], heads * vdim, device=dev)
         den = torch.zeros(rows.shape[0], heads, device=dev)
+        # The longest sequence of the step is told as the engine tells it, but not for a step that is the whole run,
+        # so that both ways of sizing the kernel's buffers are compared with each other.
         impl.mlstm(rows, offsets, i_bias, f_bias, cap, state, maxima, torch.tensor(qsl, dtype=torch.int32, device=dev),
-                   slots.to(dev), len(lengths), heads, dim, vdim, out, den)
+                   slots.to(dev), len(lengths), heads, dim, vdim, out, den, max(counts) if len(cuts) > 1 else 0)
         for i in range(len(lengths)):
             outs[i].append(out[qsl[i]:qsl[i + 1]]); dens[i].append(den[qsl[i]:qsl[i + 1]])
     return [torch.cat(o) for o in outs], [torch.cat(d) for d in dens], state, maxima
@@ -65,15 +67,19 @@ def _run_mlstm(impl, proj, lengths, cuts, slots, heads, dim, vdim, cap, i_bias, 
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads,dim,vdim", [(3, 18, 20), (1, 40, 56), (5, 4, 7), (2, 64, 32), (2, 128, 128), (1, 256, 15),
-                                             (4, 32, 48), (1, 1, 1), (2, 7, 16), (1, 200, 31)])
-def test_mlstm_in_portions_equals_whole(dtype, heads, dim, vdim):
+                                             (4, 32, 48), (1, 1, 1), (2, 7, 16), (1, 200, 31), (2, 256, 40),
+                                             (3, 8, 24), (2, 16, 8)])
+@pytest.mark.parametrize("lead", [3, 8])
+def test_mlstm_in_portions_equals_whole(dtype, heads, dim, vdim, lead):
     """Whole sequences, portions (of 1, 2 and more tokens, longer than the kernel's chunk too) and steps in which a
-    sequence brings nothing give the same read-outs and leave the same state, through slots out of order."""
+    sequence brings nothing give the same read-outs and leave the same state, through slots out of order.  `lead`:
+    the column at which q begins (8: rows and columns on 16-byte borders, which the kernel's wide loads need)."""
     from liteinfer_b200 import ops
 
     lengths, slots = (45, 6), _ints([3, 0])
-    width = 3 + 2 * heads * dim + heads * vdim + 2 * heads
-    offsets = (3, 3 + heads * dim, 3 + 2 * heads * dim, width - 2 * heads, width - heads)
+    width = lead + 2 * heads * dim + heads * vdim + 2 * heads
+    width += -width % lead
+    offsets = (lead, lead + heads * dim, lead + 2 * heads * dim, width - 2 * heads, width - heads)
     proj = [_randn(n, width, seed=20 + i, dtype=dtype) for i, n in enumerate(lengths)]
     for p in proj:
         p[:, offsets[3]:] *= 4.0                                  # gates that move: the maximum changes hands
@@ -207,7 +213,7 @@ def test_output_norm_adds_into_a_32_bit_stream_and_hands_it_back_rounded(dtype, 
 def test_sigmoid_gate_heads(dtype):
     from liteinfer_b200 import ops
 
-    for heads, size in ((4, 24), (1, 64), (7, 3), (8, 48)):
+    for heads, size in ((4, 24), (1, 64), (7, 3), (8, 48), (3, 128), (5, 4)):
         x = _randn(11, heads * size, seed=1, dtype=dtype)
         wide = _randn(11, heads + 5, seed=2, scale=3.0, dtype=dtype)
         want = x.clone()
@@ -221,10 +227,14 @@ def test_sigmoid_gate_heads(dtype):
 @pytest.mark.parametrize("heads,kv_heads,head_dim,v_dim,rot,norms,mix", [
     (4, 2, 24, 16, 12, True, True), (2, 2, 16, 16, 16, True, False), (6, 2, 8, 16, 4, True, True),
     (3, 1, 20, 28, 0, True, False), (4, 2, 64, 64, 64, True, True), (2, 1, 64, 48, 32, False, True),
-    (8, 8, 128, 128, 64, True, True), (1, 1, 40, 7, 2, True, True)])
-def test_head_norm_rotation_value_blend_and_store(dtype, heads, kv_heads, head_dim, v_dim, rot, norms, mix):
-    """Per-head norms of q and k before the rotation of the first `rot` dimensions, the blend of v with another
-    layer's values, and the pages: against the plain function, with a row of padding and pages out of order."""
+    (8, 8, 128, 128, 64, True, True), (1, 1, 40, 7, 2, True, True), (5, 1, 32, 32, 16, "q", True),
+    (3, 3, 256, 64, 128, "k", True), (2, 1, 128, 8, 0, True, False)])
+@pytest.mark.parametrize("lead", [3, 8])
+def test_head_norm_rotation_value_blend_and_store(dtype, heads, kv_heads, head_dim, v_dim, rot, norms, mix, lead):
+    """Per-head norms of q and k (or of one of them) before the rotation of the first `rot` dimensions, the blend of v
+    with another layer's values, and the pages: against the plain function, with a row of padding and pages out of
+    order.  `lead`: where the other layer's values begin in their rows (8: on a 16-byte border, so the kernel that
+    moves 16 bytes a thread runs where the sizes allow it; 3: the kernel for any layout)."""
     from liteinfer_b200 import ops
 
     page, tokens = 8, 21
@@ -233,8 +243,8 @@ def test_head_norm_rotation_value_blend_and_store(dtype, heads, kv_heads, head_d
         inv_freq = (500.0 ** (-torch.arange(0, rot, 2, dtype=torch.float32) / rot) / 3.0).to(DEV)
     width = (heads + kv_heads) * head_dim + kv_heads * v_dim
     qkv = _randn(tokens, width + 16, seed=1, scale=1.5, dtype=dtype)
-    other_wide = _randn(tokens, kv_heads * v_dim + 6, seed=2, dtype=dtype)
-    other = other_wide[:, 3:3 + kv_heads * v_dim] if mix else None
+    other_wide = _randn(tokens, kv_heads * v_dim + 16, seed=2, dtype=dtype)
+    other = other_wide[:, lead:lead + kv_heads * v_dim] if mix else None
     blend = torch.tensor([0.37], device=DEV) if mix else None
     qw, kw = (1 + 0.3 * _randn(head_dim, seed=3)).to(dtype), (1 + 0.3 * _randn(head_dim, seed=4)).to(dtype)
     positions, seq_of = _ints(list(range(30, 30 + tokens - 1)) + [0]), _ints([0] * (tokens - 1) + [-1])
@@ -242,7 +252,8 @@ def test_head_norm_rotation_value_blend_and_store(dtype, heads, kv_heads, head_d
     pools = [(torch.zeros(10, kv_heads, page, head_dim, dtype=dtype, device=DEV),
               torch.zeros(10, kv_heads, page, v_dim, dtype=dtype, device=DEV)) for _ in range(2)]
     got, want = qkv.clone(), qkv.clone()
-    args = (inv_freq, heads, kv_heads, head_dim, rot, qw if norms else None, kw if norms else None, 1e-5)
+    args = (inv_freq, heads, kv_heads, head_dim, rot, qw if norms in (True, "q") else None,
+            kw if norms in (True, "k") else None, 1e-5)
     ops.head_norm_rope_kv_write(got, positions, seq_of, table, *pools[0], *args, v_other=other, blend=blend)
     ref.head_norm_rope_kv_write(want, positions, seq_of, table, *pools[1], *args, v_other=other, blend=blend)
     q_width = heads * head_dim

@@ -310,7 +310,7 @@ def sigmoid_gate_heads_(x, gate, heads):
 
 
 def mlstm(proj, offsets, i_bias, f_bias, cap, state, maxima, query_start_loc, state_slots, num_seqs, heads, dim,
-          vdim, out, den):
+          vdim, out, den, max_query_len=0):
     """state: [slots, heads, vdim + 1, dim]: the transpose of S [dim, vdim] per head, then n; maxima: a copy of m
     per column."""
     qsl, slots = query_start_loc.tolist(), state_slots.tolist()
