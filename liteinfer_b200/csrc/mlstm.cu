@@ -13,14 +13,16 @@
 // column is a chain of its own over the tokens.  Each column also keeps its own copy of m
 // (maxima[slot][head][vdim + 1]): a block reads and writes only its own columns, so blocks of one head need
 // no order among themselves.  A block takes 16 columns of one head of one sequence; eight lanes share a column,
-// each with dim/8 of its entries in registers for the whole step, and add up their parts of the read-out with
-// three shuffles.  The tokens of a step come in chunks (16 tokens, 8 for wide heads).  A fifth warp works one
-// chunk ahead of the four that run the chain: it turns the chunk's q (scaled), k and the block's columns of v
-// into floats in shared memory, 16 bytes a load and several loads in flight, and computes the chunk's gates a
-// lane a token (the maxima by a scan whose elements are the maps m -> max(m + F, I)); the running maximum
-// stays in its registers from chunk to chunk.  Two buffers and one block-wide barrier a chunk.  Whole prompts,
-// portions and single tokens run the same code from the state the step before left.  Sequences that bring no
-// token touch nothing.
+// each with dim/8 of its entries in registers for the whole step.  The tokens of a step come in chunks (16
+// tokens, 8 for wide heads).  Warps beside the four that run the chain work one chunk ahead of them: they turn
+// the chunk's q (scaled), k and the block's columns of v into floats in shared memory, 16 bytes a load and all
+// loads of a chunk in flight at once, and the first of them computes the chunk's gates a lane a token (the
+// maxima by a scan whose elements are the maps m -> max(m + F, I)); the running maximum stays in its registers
+// from chunk to chunk.  Two buffers and one block-wide barrier a chunk.  A token's update of S needs nothing of
+// its read-out, so the chain keeps the lanes' parts of eight tokens' read-outs and adds them up together.  Whole
+// prompts, portions and single tokens run the same code from the state the step before left, and a read-out is
+// the same sum in the same order wherever its token stands in a step.  Sequences that bring no token touch
+// nothing.
 #include "common.cuh"
 
 namespace li {

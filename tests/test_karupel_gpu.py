@@ -172,19 +172,25 @@ def test_mlstm_first_token_meets_a_maximum_of_zero():
 # ------------------------------------------------------------------ norms and gates
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("heads,size,per_head,activation", [(3, 20, True, "sigmoid"), (2, 128, False, "sigmoid"),
-                                                             (5, 1, True, "silu"), (1, 48, True, "sigmoid"), (6, 48, True, "sigmoid")])
+                                                             (5, 1, True, "silu"), (1, 48, True, "sigmoid"), (7, 44, True, "sigmoid"),
+                                                             (2, 256, False, "silu"), (1, 512, True, "sigmoid"),
+                                                             (3, 260, True, "silu"), (2, 516, False, "sigmoid")])
 def test_gated_rmsnorm_with_divisor_and_weights_per_head(dtype, heads, size, per_head, activation):
+    """The gate is a column slice of a wider tensor: with rows of 9 more elements than the heads it lies on no
+    16-byte border (the element-by-element kernel), with 12 more it does (the kernel that keeps a head's row in
+    registers, for heads of up to 512)."""
     from liteinfer_b200 import ops
 
     x = _randn(13, heads * size, seed=1, scale=2.0)
-    wide = _randn(13, heads * size + 9, seed=2, dtype=dtype)
     weight = 1 + 0.2 * _randn(heads * size if per_head else size, seed=3)
     den = _randn(13, heads, seed=4).abs() + 0.05
-    for d in (None, den):
-        out, want = (torch.empty(13, heads * size, dtype=dtype, device=DEV) for _ in range(2))
-        ops.gated_rmsnorm(x, wide[:, 4:4 + heads * size], weight, 1e-5, out, heads, gate_activation=activation, den=d)
-        ref.gated_rmsnorm(x, wide[:, 4:4 + heads * size], weight, 1e-5, want, heads, gate_activation=activation, den=d)
-        torch.testing.assert_close(out.float(), want.float(), **_tol(dtype))
+    for spare in (9, 12):
+        wide = _randn(13, heads * size + spare, seed=2, dtype=dtype)
+        for d in (None, den):
+            out, want = (torch.empty(13, heads * size, dtype=dtype, device=DEV) for _ in range(2))
+            ops.gated_rmsnorm(x, wide[:, 4:4 + heads * size], weight, 1e-5, out, heads, gate_activation=activation, den=d)
+            ref.gated_rmsnorm(x, wide[:, 4:4 + heads * size], weight, 1e-5, want, heads, gate_activation=activation, den=d)
+            torch.testing.assert_close(out.float(), want.float(), **_tol(dtype))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
