@@ -20,8 +20,9 @@
 // maxima by a scan whose elements are the maps m -> max(m + F, I)); the running maximum stays in its registers
 // from chunk to chunk.  Two buffers and one block-wide barrier a chunk.  A token's update of S needs nothing of
 // its read-out, so the chain keeps the lanes' parts of eight tokens' read-outs and adds them up together.  Whole
-// prompts, portions and single tokens run the same code from the state the step before left, and a read-out is
-// the same sum in the same order wherever its token stands in a step.  Sequences that bring no token touch
+// prompts, portions and single tokens run the same code from the state the step before left (in a step of single
+// tokens the chain's threads fetch their token themselves and the fifth warp has only the gates), and a read-out
+// is the same sum in the same order wherever its token stands in a step.  Sequences that bring no token touch
 // nothing.
 #include "common.cuh"
 
@@ -129,7 +130,7 @@ __device__ __forceinline__ float mlstm_token(float (&S)[NPL], const float* __res
 // NPL: entries of a column a lane keeps.  VEC: the lane's entries are float4 groups 4 * (sub + 8 j) .. + 3
 // (dim a multiple of four, 16-byte aligned state); otherwise entries sub + 8 i.
 template <typename T, int NPL, bool VEC, int U>
-__global__ void __launch_bounds__(kMlstmThreads)
+__global__ void __launch_bounds__(U == 1 ? 160 : kMlstmThreads, U == 1 && NPL <= 16 ? 6 : (NPL <= 16 ? 3 : 2))
 mlstm_kernel(const T* __restrict__ proj, size_t row_stride, int q_off, int k_off, int v_off, int i_off, int f_off,
              const float* __restrict__ i_bias, const float* __restrict__ f_bias, float cap,
              float* __restrict__ state, float* __restrict__ maxima, const int* __restrict__ query_start_loc,
@@ -185,8 +186,9 @@ mlstm_kernel(const T* __restrict__ proj, size_t row_stride, int q_off, int k_off
           raw_i = to_float(row[i_off + head]);
           raw_f = to_float(row[f_off + head]);
         }
-        mlstm_fill<T, U>(qs, ks, vs, proj, row_stride, q_off + head * dim, k_off + head * dim, v_off + head * vdim,
-                         first_column, t0, n, dim, dimp, vdim, scale, vec_in != 0, who, team);
+        if (U > 1)
+          mlstm_fill<T, U>(qs, ks, vs, proj, row_stride, q_off + head * dim, k_off + head * dim, v_off + head * vdim,
+                           first_column, t0, n, dim, dimp, vdim, scale, vec_in != 0, who, team);
         if (gates) {
           const float gate_i = has ? cap * tanhf((raw_i + bias_i) / cap) : 0.f;
           const float gate_f = has ? log_sigmoid(cap * tanhf((raw_f + bias_f) / cap)) : 0.f;
@@ -252,9 +254,17 @@ mlstm_kernel(const T* __restrict__ proj, size_t row_stride, int q_off, int k_off
                          : out + (size_t)begin * heads * vdim + (size_t)head * vdim + (live ? column : 0);
 
   for (int c = 0; c < chunks; ++c) {
-    __syncthreads();      // chunk c is ready
     const int t0 = begin + c * chunk;
     const int n = end - t0 < chunk ? end - t0 : chunk;
+    if (U == 1) {
+      // Chunks of one (a step of single tokens): the chain's own threads fetch the token, beside their loads of
+      // the state, while the fifth warp computes its gates.
+      float* qw = shared + (c & 1) * per_buffer;
+      mlstm_fill<T, 1>(qw, qw + chunk * dimp, qw + 2 * chunk * dimp, proj, row_stride, q_off + head * dim,
+                       k_off + head * dim, v_off + head * vdim, first_column, t0, n, dim, dimp, vdim,
+                       rsqrtf((float)dim), vec_in != 0, tid, 128);
+    }
+    __syncthreads();      // chunk c is ready
     const float* qs = shared + (c & 1) * per_buffer;
     const float* ks = qs + chunk * dimp;
     const float* vs = ks + chunk * dimp + group;
