@@ -7,6 +7,9 @@ KAR_B: starts with the delta layer; one attention that names value mixing alone 
 rotation; an mLSTM of one head; convolutions of one tap; values wider than keys.
 KAR_C: sizes that the tensor-core attention and the vector forms of the recurrences take (keys and values of 64),
 every dimension rotated without scaling, an attention without value mixing between two with it.
+KAR_D: small sizes that are multiples of little (width 36, heads of 6 and 10): an mLSTM first and last, two
+attentions in a row of which the first mixes nothing and rotates two dimensions, a source and a mixed layer with
+heads of different key sizes but equal values, three q/k heads for six value heads in the delta layer, two taps.
 """
 
 import random
@@ -57,8 +60,26 @@ KAR_C = {
     ],
 }
 
+KAR_D = {
+    "architecture": "Karupel", "vocab": 97, "width": 36, "norm": {"eps": 1e-4},
+    "layers": [
+        {"type": "mlstm", "mlp": {"kind": "dense", "ff": 20}, "mixer": {"heads": 2, "dim": 6, "vdim": 10, "gate_cap": 5.0}},
+        {"type": "attention", "mlp": None,
+         "mixer": {"heads": 3, "kv_heads": 3, "dim": 6, "vdim": 10, "scale": 0.5,
+                   "rot": {"dims": 2, "base": 37.0, "scaling": None}}},
+        {"type": "attention", "mlp": {"kind": "dense", "ff": 28},
+         "mixer": {"heads": 4, "kv_heads": 2, "dim": 12, "vdim": 4, "scale": 0.2, "v_mix": True,
+                   "rot": {"dims": 12, "base": 900.0, "scaling": {"factor": 8.0}}}},
+        {"type": "delta", "mlp": {"kind": "dense", "ff": 12},
+         "mixer": {"heads": 6, "kv_heads": 3, "dim": 4, "vdim": 6, "conv": 2}},
+        {"type": "attention", "mlp": None,
+         "mixer": {"heads": 2, "kv_heads": 2, "dim": 10, "vdim": 4, "scale": 0.33, "v_mix": True}},
+        {"type": "mlstm", "mlp": None, "mixer": {"heads": 3, "dim": 12, "vdim": 12, "gate_cap": 30.0}},
+    ],
+}
+
 # name -> (config, seed, page size)
-ALL = {"kar_a": (KAR_A, 21, 16), "kar_b": (KAR_B, 22, 4), "kar_c": (KAR_C, 23, 16)}
+ALL = {"kar_a": (KAR_A, 21, 16), "kar_b": (KAR_B, 22, 4), "kar_c": (KAR_C, 23, 16), "kar_d": (KAR_D, 24, 8)}
 
 
 def prompt(vocab: int, length: int, seed: int) -> list[int]:
@@ -67,6 +88,6 @@ def prompt(vocab: int, length: int, seed: int) -> list[int]:
 
 
 # Largest absolute difference of float32 logits from the float64 plain implementation that rounding alone explains.
-FLOAT32_TOLERANCE = {"kar_a": 5e-5, "kar_b": 5e-5, "kar_c": 1e-4}
+FLOAT32_TOLERANCE = {"kar_a": 5e-5, "kar_b": 5e-5, "kar_c": 1e-4, "kar_d": 5e-5}
 # The same for bfloat16 (products' operands, pages and the sublayers' outputs are rounded; logits are of size 1).
-BFLOAT16_TOLERANCE = {"kar_a": 0.08, "kar_b": 0.08, "kar_c": 0.1}
+BFLOAT16_TOLERANCE = {"kar_a": 0.08, "kar_b": 0.08, "kar_c": 0.1, "kar_d": 0.08}

@@ -58,7 +58,8 @@ def test_config_round_trip_and_names(karupel_dirs):
         resolve(bad)
 
 
-@pytest.mark.parametrize("name,lengths", [("kar_a", (1, 7, 61, 75)), ("kar_b", (2, 30, 45)), ("kar_c", (3, 70, 40, 18, 52))])
+@pytest.mark.parametrize("name,lengths", [("kar_a", (1, 7, 61, 75)), ("kar_b", (2, 30, 45)), ("kar_c", (3, 70, 40, 18, 52)),
+                                           ("kar_d", (4, 33, 58, 21))])
 def test_all_cuts_match_plain_on_cpu(cpu_kernels, karupel_dirs, name, lengths):
     from liteinfer_b200.engine.loading import build_runner
 

@@ -289,7 +289,8 @@ def _expected(model_dir, requests):
     return {name: plain_karupel.forward(config, tensors, tokens).float() for name, tokens in requests.items()}
 
 
-@pytest.mark.parametrize("name,lengths", [("kar_a", (1, 7, 61, 90)), ("kar_b", (2, 30, 45)), ("kar_c", (5, 52, 150, 18, 210))])
+@pytest.mark.parametrize("name,lengths", [("kar_a", (1, 7, 61, 90)), ("kar_b", (2, 30, 45)), ("kar_c", (5, 52, 150, 18, 210)),
+                                           ("kar_d", (4, 33, 58, 21))])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_replay_all_cuts(karupel_dirs, tmp_path, name, lengths, dtype):
     """Whole, the tail decoded, portions down to two tokens, four live requests whose pages and slots are used
