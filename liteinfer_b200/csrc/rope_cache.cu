@@ -164,15 +164,30 @@ head_norm_rope_kv_write_vec_kernel(T* __restrict__ qkv, size_t row_stride, const
 #pragma unroll
       for (int e = 0; e < N; ++e) x[e] = x[e] * inv * wv[e];
     }
+    // Both halves of a pair are x * cos + partner * (-+ sin), and a dimension that is not rotated is x * 1 +
+    // x * 0: the lane fetches its eight cosines and sines (the sign in them) by 16-byte reads once, and every
+    // element is the same two products and one sum, rounded as `rotate_lo` / `rotate_hi` round them.
     const int from = j0 < half ? lane + apart : (j0 < rotary_dim ? lane - apart : lane);
+    float c[N], sn[N];
+    if (j0 < rotary_dim) {
+      const int at = j0 < half ? j0 : j0 - half;
+      const float sign = j0 < half ? -1.0f : 1.0f;
+#pragma unroll
+      for (int e = 0; e < N; e += 4) {
+        const float4 cv = *reinterpret_cast<const float4*>(cosv + at + e);
+        const float4 sv = *reinterpret_cast<const float4*>(sinv + at + e);
+        c[e] = cv.x; c[e + 1] = cv.y; c[e + 2] = cv.z; c[e + 3] = cv.w;
+        sn[e] = sign * sv.x; sn[e + 1] = sign * sv.y; sn[e + 2] = sign * sv.z; sn[e + 3] = sign * sv.w;
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < N; ++e) { c[e] = 1.0f; sn[e] = 0.f; }
+    }
     Vec16<T> result;
 #pragma unroll
     for (int e = 0; e < N; ++e) {
       const float y = __shfl_sync(0xffffffffu, x[e], from);
-      float r = x[e];
-      if (j0 < half) r = rotate_lo(x[e], y, cosv[j0 + e], sinv[j0 + e]);
-      else if (j0 < rotary_dim) r = rotate_hi(y, x[e], cosv[j0 - half + e], sinv[j0 - half + e]);
-      result.set(e, r);
+      result.set(e, j0 < rotary_dim ? __fadd_rn(__fmul_rn(x[e], c[e]), __fmul_rn(y, sn[e])) : x[e]);
     }
     if (active && (is_q || store)) {
       T* dst = is_q ? p : k_pool + (((size_t)page * kv_heads + (h - heads)) * page_size + slot) * head_dim + j0;
