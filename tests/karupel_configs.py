@@ -10,6 +10,8 @@ every dimension rotated without scaling, an attention without value mixing betwe
 KAR_D: small sizes that are multiples of little (width 36, heads of 6 and 10): an mLSTM first and last, two
 attentions in a row of which the first mixes nothing and rotates two dimensions, a source and a mixed layer with
 heads of different key sizes but equal values, three q/k heads for six value heads in the delta layer, two taps.
+KAR_E: a width of 512 with heads of 128 x 128, where prompts of a few hundred tokens take the tensor-core products
+and attention and the recurrences' widest register forms.
 """
 
 import random
@@ -78,8 +80,22 @@ KAR_D = {
     ],
 }
 
+KAR_E = {
+    "architecture": "Karupel", "vocab": 1500, "width": 512, "norm": {"eps": 1e-5},
+    "layers": [
+        {"type": "mlstm", "mlp": {"kind": "dense", "ff": 1024}, "mixer": {"heads": 4, "dim": 128, "vdim": 128, "gate_cap": 15.0}},
+        {"type": "attention", "mlp": {"kind": "dense", "ff": 768},
+         "mixer": {"heads": 8, "kv_heads": 2, "dim": 128, "vdim": 128, "scale": 0.088, "v_mix": True,
+                   "rot": {"dims": 64, "base": 10000.0, "scaling": {"factor": 4.0}}}},
+        {"type": "delta", "mlp": None, "mixer": {"heads": 4, "kv_heads": 2, "dim": 128, "vdim": 128, "conv": 4}},
+        {"type": "attention", "mlp": {"kind": "dense", "ff": 1024},
+         "mixer": {"heads": 8, "kv_heads": 2, "dim": 128, "vdim": 128, "scale": 0.1, "v_mix": True,
+                   "rot": {"dims": 128, "base": 20000.0, "scaling": None}}},
+    ],
+}
+
 # name -> (config, seed, page size)
-ALL = {"kar_a": (KAR_A, 21, 16), "kar_b": (KAR_B, 22, 4), "kar_c": (KAR_C, 23, 16), "kar_d": (KAR_D, 24, 8)}
+ALL = {"kar_a": (KAR_A, 21, 16), "kar_b": (KAR_B, 22, 4), "kar_c": (KAR_C, 23, 16), "kar_d": (KAR_D, 24, 8), "kar_e": (KAR_E, 25, 16)}
 
 
 def prompt(vocab: int, length: int, seed: int) -> list[int]:
@@ -88,6 +104,11 @@ def prompt(vocab: int, length: int, seed: int) -> list[int]:
 
 
 # Largest absolute difference of float32 logits from the float64 plain implementation that rounding alone explains.
-FLOAT32_TOLERANCE = {"kar_a": 5e-5, "kar_b": 5e-5, "kar_c": 1e-4, "kar_d": 5e-5}
+FLOAT32_TOLERANCE = {"kar_a": 5e-5, "kar_b": 5e-5, "kar_c": 1e-4, "kar_d": 5e-5, "kar_e": 2e-4}
 # The same for bfloat16 (products' operands, pages and the sublayers' outputs are rounded; logits are of size 1).
-BFLOAT16_TOLERANCE = {"kar_a": 0.08, "kar_b": 0.08, "kar_c": 0.1, "kar_d": 0.08}
+BFLOAT16_TOLERANCE = {"kar_a": 0.08, "kar_b": 0.08, "kar_c": 0.1, "kar_d": 0.08, "kar_e": 0.6}
+# kar_e: at a few positions the mLSTM's divisor |n . q| is a difference of near-equal numbers and multiplies
+# bfloat16's rounding tenfold (the same positions lead the 32-bit run's errors); what holds the bfloat16 run of that
+# configuration to account is the typical position: the median over all wanted positions of the difference's root
+# mean square (mean taken off) over the logits' standard deviation.
+BFLOAT16_TYPICAL = {"kar_e": 0.03}
