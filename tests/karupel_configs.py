@@ -98,6 +98,20 @@ KAR_E = {
 ALL = {"kar_a": (KAR_A, 21, 16), "kar_b": (KAR_B, 22, 4), "kar_c": (KAR_C, 23, 16), "kar_d": (KAR_D, 24, 8), "kar_e": (KAR_E, 25, 16)}
 
 
+def only(kinds) -> dict:
+    """A configuration whose layers are the given kinds of mixer, twice over (vocabulary 61)."""
+    mixers = {
+        "mlstm": {"type": "mlstm", "mlp": None, "mixer": {"heads": 2, "dim": 10, "vdim": 6, "gate_cap": 6.0}},
+        "delta": {"type": "delta", "mlp": {"kind": "dense", "ff": 24},
+                  "mixer": {"heads": 2, "kv_heads": 1, "dim": 6, "vdim": 10, "conv": 3}},
+        "attention": {"type": "attention", "mlp": {"kind": "dense", "ff": 16},
+                      "mixer": {"heads": 2, "kv_heads": 1, "dim": 6, "vdim": 8, "scale": 0.4,
+                                "rot": {"dims": 4, "base": 50.0, "scaling": {"factor": 3.0}}}},
+    }
+    return {"architecture": "Karupel", "vocab": 61, "width": 20, "norm": {"eps": 1e-5},
+            "layers": [mixers[k] for k in kinds] * 2}
+
+
 def prompt(vocab: int, length: int, seed: int) -> list[int]:
     rng = random.Random(seed)
     return [rng.randrange(vocab) for _ in range(length)]

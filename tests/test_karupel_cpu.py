@@ -128,3 +128,21 @@ def test_greedy_generation_through_the_engine(cpu_kernels, karupel_dirs):
         for _ in range(6):
             tokens.append(int(plain_karupel.forward(config, tensors, tokens)[-1].argmax()))
         assert list(output.token_ids) == tokens[len(prompt):]
+
+
+@pytest.mark.parametrize("kinds", [("mlstm", "delta"), ("attention",), ("delta",), ("mlstm",)])
+def test_models_of_some_mixers_only(cpu_kernels, tmp_path, kinds):
+    """A model without attention layers keeps no pages, one without recurrent layers no state: both run, cut every
+    way, like the plain implementation."""
+    from liteinfer_b200.engine.loading import build_runner
+    from liteinfer_b200.weights.random_init import write_random_model
+
+    config = kc.only(kinds)
+    model_dir = write_random_model(config, tmp_path / "model", 31)
+    requests = {f"r{i}": kc.prompt(61, n, 7 + i) for i, n in enumerate((3, 26, 41))}
+    expected = expected_logits(model_dir, requests)
+    trace = full_trace(requests)
+    runner = build_runner(model_dir, torch.float32, "cpu", 4, -(-trace.max_tokens // 4), 4)
+    results = rh.run_in_process(runner, trace)
+    worst, where = rh.worst_error(results, rh.gather_expected(trace, expected))
+    assert worst < 5e-5, f"worst difference {worst} at step {where}"

@@ -321,6 +321,26 @@ def test_trace_replay_all_cuts(karupel_dirs, tmp_path, name, lengths, dtype):
         assert typical < kc.BFLOAT16_TYPICAL[name], f"typical relative difference {typical}"
 
 
+@pytest.mark.parametrize("kinds", [("mlstm", "delta"), ("attention",)])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_models_of_some_mixers_only(tmp_path, kinds, dtype):
+    """A model without attention layers keeps no pages, one without recurrent layers no state: both run through the
+    trace runner, whole, in portions and token by token, like the plain implementation."""
+    from liteinfer_b200.weights.random_init import write_random_model
+
+    model_dir = write_random_model(kc.only(kinds), tmp_path / "model", 31)
+    requests = {f"r{i}": kc.prompt(61, n, 7 + i) for i, n in enumerate((3, 26, 41))}
+    expected = _expected(model_dir, requests)
+    trace = rh.Trace()
+    rh.whole(trace, requests)
+    rh.tail_decoded(trace, requests, tail=40)
+    rh.portions(trace, requests)
+    rh.mixed(trace, requests)
+    results = rh.run_program(trace, model_dir, dtype, tmp_path / "out", 61, page_size=4)
+    worst, where = rh.worst_error(results, rh.gather_expected(trace, expected))
+    assert worst < (1e-4 if dtype == "float32" else 0.08), f"worst difference {worst} at step {where}"
+
+
 def test_layers_one_by_one_against_plain(karupel_dirs):
     """The residual stream after every layer (32-bit engine) equals the plain implementation's."""
     from liteinfer_b200.engine.loading import build_runner
