@@ -71,7 +71,7 @@ class KarupelMixer:
         if kind == "delta":
             return cls(kind, conv=_need(raw, "conv", int, where), **sizes)
         rot = None
-        if raw.get("rot"):
+        if raw.get("rot") and raw["rot"].get("dims") != 0:      # no dimension rotated: as good as no rotation
             r = raw["rot"]
             factor = _need(r["scaling"], "factor", float, where + " rot.scaling") if r.get("scaling") else None
             rot = KarupelRotation(_need(r, "dims", int, where + " rot"), _need(r, "base", float, where + " rot"), factor)
