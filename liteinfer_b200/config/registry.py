@@ -38,6 +38,7 @@ def _builtins() -> None:
     import liteinfer_b200.architectures.gifudra  # noqa: F401  (registers Gifudra)
     import liteinfer_b200.architectures.karupel  # noqa: F401  (registers Karupel)
     import liteinfer_b200.architectures.kegizen  # noqa: F401  (registers Kegizen)
+    import liteinfer_b200.architectures.kutolix  # noqa: F401  (registers Kutolix)
     import liteinfer_b200.architectures.llama  # noqa: F401  (registers LlamaForCausalLM)
 
 

@@ -12,7 +12,8 @@
 //
 // Options: values of another size than keys (`v_dim`; out then has heads * v_dim columns); with a window, the
 // first `keep_first` keys of a sequence stay visible behind it (they are walked first, then the window's keys);
-// `softcap` > 0 turns a scaled score s into softcap * tanh(s / softcap) before the softmax.
+// `softcap` > 0 turns a scaled score s into softcap * tanh(s / softcap) before the softmax; `sink` [heads]
+// (float, optional): exp(sink[h]) is one more term of head h's denominator, with no key and no value.
 //
 // Work split: block = (query tile, KV head, sequence); its warps take the rows
 // (query, head-in-group) of the tile in turn, one row per warp at a time.  A row
@@ -35,7 +36,8 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_row_stride, T* __r
                                const int* __restrict__ block_table, int table_stride,
                                const int* __restrict__ query_start_loc, const int* __restrict__ context_lens,
                                int heads, int kv_heads, int head_dim, int v_dim, int page_size, int num_pages,
-                               float scale, int window, int keep_first, float softcap) {
+                               float scale, int window, int keep_first, float softcap,
+                               const float* __restrict__ sink) {
   extern __shared__ float q_smem[];  // [warps][head_dim]
   const int seq = blockIdx.z, kvh = blockIdx.y;
   const int q_begin = query_start_loc[seq], q_len = query_start_loc[seq + 1] - q_begin;
@@ -111,6 +113,14 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_row_stride, T* __r
         m = m_new;
       }
     }
+    if (sink != nullptr) {      // one more term of the denominator: it has no key, no value, and is not scaled
+      const float sk = sink[head];
+      const float m_new = fmaxf(m, sk);
+      const float alpha = expf(m - m_new);
+      l = l * alpha + expf(sk - m_new);
+#pragma unroll
+      for (int i = 0; i < kDimsPerLane; ++i) acc[i] *= alpha;
+    }
     T* orow = out + (size_t)(q_begin + qi) * out_row_stride + (size_t)head * v_dim;
     const float inv = l > 0.f ? 1.0f / l : 0.f;
 #pragma unroll
@@ -127,13 +137,14 @@ using namespace li;
 
 // q: [tokens, q_row_stride] with head h of a token at columns [h*head_dim, (h+1)*head_dim).
 // out: [tokens, out_row_stride] with head h at columns [h*v_dim, (h+1)*v_dim).  k_pool: [num_pages, kv_heads,
-// page_size, head_dim]; v_pool likewise with v_dim.  window <= 0: every earlier key is visible.
+// page_size, head_dim]; v_pool likewise with v_dim.  window <= 0: every earlier key is visible.  sink: null or [heads].
 LI_EXPORT int li_paged_attention_generic(int dtype, const void* q, int q_row_stride, void* out, int out_row_stride,
                                          const void* k_pool, const void* v_pool, const int* block_table,
                                          int table_stride, const int* query_start_loc, const int* context_lens,
                                          int num_seqs, int max_q_len, int heads, int kv_heads, int head_dim,
                                          int v_dim, int page_size, int num_pages, float scale, int window,
-                                         int keep_first, float softcap, cudaStream_t stream) {
+                                         int keep_first, float softcap, const float* sink,
+                                         cudaStream_t stream) {
   if (num_seqs == 0 || max_q_len == 0) return 0;
   if (head_dim < 1 || head_dim > kMaxHeadDim || kv_heads < 1 || heads % kv_heads) return LI_ERR_UNSUPPORTED;
   if (v_dim < 1 || v_dim > kMaxHeadDim) return LI_ERR_UNSUPPORTED;
@@ -145,11 +156,11 @@ LI_EXPORT int li_paged_attention_generic(int dtype, const void* q, int q_row_str
     paged_attention_generic_kernel<float><<<grid, threads, smem, stream>>>(
         (const float*)q, q_row_stride, (float*)out, out_row_stride, (const float*)k_pool, (const float*)v_pool,
         block_table, table_stride, query_start_loc, context_lens, heads, kv_heads, head_dim, v_dim, page_size,
-        num_pages, scale, window, keep_first, softcap);
+        num_pages, scale, window, keep_first, softcap, sink);
   else
     paged_attention_generic_kernel<bf16><<<grid, threads, smem, stream>>>(
         (const bf16*)q, q_row_stride, (bf16*)out, out_row_stride, (const bf16*)k_pool, (const bf16*)v_pool,
         block_table, table_stride, query_start_loc, context_lens, heads, kv_heads, head_dim, v_dim, page_size,
-        num_pages, scale, window, keep_first, softcap);
+        num_pages, scale, window, keep_first, softcap, sink);
   LI_LAUNCH_CHECK();
 }

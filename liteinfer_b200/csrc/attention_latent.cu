@@ -32,7 +32,7 @@ latent_prep_kernel(const T* __restrict__ proj, int proj_stride, int q_off, int q
                    int rot_dim, int rot_dims, const float* __restrict__ q_weight, const float* __restrict__ kv_weight,
                    float eps, const float* __restrict__ inv_freq, const int* __restrict__ positions,
                    const int* __restrict__ seq_of_token, const int* __restrict__ block_table, int table_stride,
-                   T* __restrict__ pool, int page_size, int num_pages, T* __restrict__ q_out) {
+                   T* __restrict__ pool, int page_size, int num_pages, T* __restrict__ q_out, float cs_scale) {
   __shared__ float scratch[33];
   const int t = blockIdx.x;
   grid_launch_dependents();
@@ -71,7 +71,7 @@ latent_prep_kernel(const T* __restrict__ proj, int proj_stride, int q_off, int q
   const int half = rot_dims / 2;
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
     const float angle = __fmul_rn((float)pos, inv_freq[i]);
-    const float c = cosf(angle), s = sinf(angle);
+    const float c = cosf(angle) * cs_scale, s = sinf(angle) * cs_scale;
     const float a = to_float(shared[i]), b = to_float(shared[i + half]);
     entry[kv_rank + i] = from_float<T>(rotate_lo(a, b, c, s));
     entry[kv_rank + i + half] = from_float<T>(rotate_hi(a, b, c, s));
@@ -92,7 +92,8 @@ latent_attention_kernel(const T* __restrict__ q_lat, long q_lat_head_stride, int
                         const T* __restrict__ pool, const int* __restrict__ block_table, int table_stride,
                         const int* __restrict__ query_start_loc, const int* __restrict__ context_lens,
                         const float* __restrict__ inv_freq, const float* __restrict__ sink, int heads, int kv_rank,
-                        int rot_dim, int rot_dims, int page_size, int num_pages, float scale) {
+                        int rot_dim, int rot_dims, int page_size, int num_pages, float scale, int window,
+                        float cs_scale) {
   extern __shared__ float q_smem[];  // [warps][kv_rank + rot_dim]
   const int seq = blockIdx.z;
   grid_launch_dependents();
@@ -122,7 +123,7 @@ latent_attention_kernel(const T* __restrict__ q_lat, long q_lat_head_stride, int
     for (int d = lane; d < kv_rank; d += 32) qs[d] = to_float(ql[d]);
     for (int i = lane; i < half; i += 32) {
       const float angle = __fmul_rn((float)qpos, inv_freq[i]);
-      const float c = cosf(angle), s = sinf(angle);
+      const float c = cosf(angle) * cs_scale, s = sinf(angle) * cs_scale;
       const float a = to_float(qr[i]), b = to_float(qr[i + half]);
       // The rotated query takes the rounding a stored tensor of the engine's dtype would give it, as the key's does.
       qs[kv_rank + i] = round_to<T>(rotate_lo(a, b, c, s));
@@ -136,11 +137,14 @@ latent_attention_kernel(const T* __restrict__ q_lat, long q_lat_head_stride, int
 #pragma unroll
     for (int i = 0; i < kPerLane; ++i) acc[i] = 0.f;
 
-    for (int base = 0; base <= qpos; base += 32) {
+    // With a window the walk starts at the first visible key rounded down to a multiple of 32: the order of every
+    // sum still depends on the row's position only.
+    const int first = window > 0 ? max(qpos - window + 1, 0) : 0;
+    for (int base = (first / 32) * 32; base <= qpos; base += 32) {
       const int kpos = base + lane;
       long erow = -1;       // index of this lane's entry inside the pool: page * page_size + slot
       float s = -INFINITY;
-      if (kpos <= qpos) {
+      if (kpos >= first && kpos <= qpos) {
         const int page = table[kpos / page_size];
         if (page >= 0 && page < num_pages) {
           erow = (long)page * page_size + kpos % page_size;
@@ -215,12 +219,13 @@ using namespace li;
 // proj [tokens, proj_stride]: the query's down projection at columns [q_off, q_off + q_rank), the key/value down
 // projection ([latent | shared key part]) at [kv_off, kv_off + kv_rank + rot_dim); kv_off < 0: the layer makes
 // no entries of its own.  q_out [tokens, q_rank] (null: skipped).  pool [num_pages, page_size, kv_rank + rot_dim];
-// num_pages 0: nothing is stored.  inv_freq [rot_dims / 2] float; q_weight, kv_weight float.
+// num_pages 0: nothing is stored.  inv_freq [rot_dims / 2] float; q_weight, kv_weight float.  cos_sin_scale multiplies
+// every cosine and sine of the rotation.
 LI_EXPORT int li_latent_prep(int dtype, const void* proj, int proj_stride, int q_off, int q_rank, int kv_off,
                              int kv_rank, int rot_dim, int rot_dims, const float* q_weight, const float* kv_weight,
                              float eps, const float* inv_freq, const int* positions, const int* seq_of_token,
                              const int* block_table, int table_stride, void* pool, int page_size, int num_pages,
-                             void* q_out, int tokens, cudaStream_t stream) {
+                             void* q_out, int tokens, float cos_sin_scale, cudaStream_t stream) {
   if (tokens == 0) return 0;
   if (rot_dims < 0 || rot_dims > rot_dim || (rot_dims & 1)) return LI_ERR_UNSUPPORTED;
   cudaError_t e;
@@ -228,26 +233,28 @@ LI_EXPORT int li_latent_prep(int dtype, const void* proj, int proj_stride, int q
     e = launch_pdl(tokens, latent_prep_kernel<float>, dim3(tokens), dim3(128), 0, stream, (const float*)proj,
                    proj_stride, q_off, q_rank, kv_off, kv_rank, rot_dim, rot_dims, q_weight, kv_weight, eps, inv_freq,
                    positions, seq_of_token, block_table, table_stride, (float*)pool, page_size, num_pages,
-                   (float*)q_out);
+                   (float*)q_out, cos_sin_scale);
   else
     e = launch_pdl(tokens, latent_prep_kernel<bf16>, dim3(tokens), dim3(128), 0, stream, (const bf16*)proj,
                    proj_stride, q_off, q_rank, kv_off, kv_rank, rot_dim, rot_dims, q_weight, kv_weight, eps, inv_freq,
                    positions, seq_of_token, block_table, table_stride, (bf16*)pool, page_size, num_pages,
-                   (bf16*)q_out);
+                   (bf16*)q_out, cos_sin_scale);
   return (int)e;
 }
 
 // q_lat: the absorbed queries, head h of token t at q_lat + h * q_lat_head_stride + t * q_lat_token_stride
 // (kv_rank numbers).  q_raw: the query projection, the part of head h of token t that turns at
 // q_raw + t * q_raw_token_stride + h * q_raw_head_stride + q_rot_off (rot_dim numbers, not yet rotated).
-// out: like q_lat.  sink [heads] float or null.
+// out: like q_lat.  sink [heads] float or null.  window > 0: the query at position i sees the keys j with
+// 0 <= i - j < window.  cos_sin_scale multiplies every cosine and sine of the query's rotation.
 LI_EXPORT int li_latent_attention(int dtype, const void* q_lat, long q_lat_head_stride, int q_lat_token_stride,
                                   const void* q_raw, int q_raw_token_stride, int q_raw_head_stride, int q_rot_off,
                                   void* out, long out_head_stride, int out_token_stride, const void* pool,
                                   const int* block_table, int table_stride, const int* query_start_loc,
                                   const int* context_lens, const float* inv_freq, const float* sink, int num_seqs,
                                   int max_q_len, int heads, int kv_rank, int rot_dim, int rot_dims, int page_size,
-                                  int num_pages, float scale, cudaStream_t stream) {
+                                  int num_pages, float scale, int window, float cos_sin_scale,
+                                  cudaStream_t stream) {
   if (num_seqs == 0 || max_q_len == 0) return 0;
   if (kv_rank < 1 || kv_rank > kMaxLatent || rot_dim < 0 || rot_dims > rot_dim || (rot_dims & 1)) return LI_ERR_UNSUPPORTED;
   if (num_seqs > 65535) return LI_ERR_UNSUPPORTED;
@@ -261,7 +268,7 @@ LI_EXPORT int li_latent_attention(int dtype, const void* q_lat, long q_lat_head_
                  q_lat_head_stride, q_lat_token_stride, (const T*)q_raw, q_raw_token_stride, q_raw_head_stride,       \
                  q_rot_off, (T*)out, out_head_stride, out_token_stride, (const T*)pool, block_table, table_stride,    \
                  query_start_loc, context_lens, inv_freq, sink, heads, kv_rank, rot_dim, rot_dims, page_size,         \
-                 num_pages, scale)
+                 num_pages, scale, window, cos_sin_scale)
   if (dtype == kFloat32) {
     if (kv_rank <= 512) LI_LATENT_LAUNCH(float, 16); else LI_LATENT_LAUNCH(float, 32);
   } else {

@@ -43,6 +43,8 @@ struct LatentParams {
   float* partial_lse;           // [splits][heads][tokens], in units of log2
   int tokens;
   int* error_flag;              // set to 31 if a wait for a tile of entries ever gave up (may be null)
+  int window;                   // > 0: the query at position i sees the keys j with 0 <= i - j < window
+  float cs_scale;               // multiplies every cosine and sine of the query's rotation
 };
 
 // One entry (a contiguous run of bytes, 16-byte aligned at both ends) from global into shared memory by the copy
@@ -155,8 +157,10 @@ latent_attention_mma_kernel(const LatentParams p) {
   const int first_pos = ctx - q_len + query0;                        // position of the block's first query
   const int last_pos = min(first_pos + MT - 1, ctx - 1);             // of its last one: the keys end there
   const int all_tiles = last_pos / KI + 1;                           // rounds of KI keys
-  const int per_split = (all_tiles + p.num_splits - 1) / p.num_splits;
-  const int tile_begin = split * per_split, tile_end = min(all_tiles, tile_begin + per_split);
+  // With a window the first round is the one that holds the first key the block's first query still sees.
+  const int tile_first = p.window > 0 ? max(first_pos - p.window + 1, 0) / KI : 0;
+  const int per_split = (all_tiles - tile_first + p.num_splits - 1) / p.num_splits;
+  const int tile_begin = tile_first + split * per_split, tile_end = min(all_tiles, tile_begin + per_split);
 
   const unsigned bars = smem_addr(stage_bars);
   if (threadIdx.x == 0) {
@@ -199,7 +203,7 @@ latent_attention_mma_kernel(const LatentParams p) {
         if (d < p.rot_dims) {
           const int j = d < half ? d : d - half;
           const float angle = __fmul_rn((float)(first_pos + row / 16), p.inv_freq[j]);
-          const float c = cosf(angle), s = sinf(angle);
+          const float c = cosf(angle) * p.cs_scale, s = sinf(angle) * p.cs_scale;
           const float a = to_float(qr[j]), b = to_float(qr[j + half]);
           v = d < half ? rotate_lo(a, b, c, s) : rotate_hi(a, b, c, s);
         } else {
@@ -339,7 +343,7 @@ latent_attention_mma_kernel(const LatentParams p) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int key = kcol + (e & 1);
-          sc[j][e] = key <= pos ? sc[j][e] * p.scale_log2 : -INFINITY;
+          sc[j][e] = (key <= pos && (p.window <= 0 || key > pos - p.window)) ? sc[j][e] * p.scale_log2 : -INFINITY;
         }
         float m_lo = fmaxf(sc[j][0], sc[j][1]), m_hi = fmaxf(sc[j][2], sc[j][3]);
         m_lo = fmaxf(m_lo, __shfl_xor_sync(0xffffffffu, m_lo, 1));
@@ -595,7 +599,8 @@ LI_EXPORT int li_latent_attention_mma_supports(int kv_rank, int rot_dim, int rot
 // [num_seqs] or null: the batch rows to run (-1: none); max_q_len 1 runs the single-token form, whose keys
 // `num_splits` blocks share (partial_out [splits, heads, tokens, kv_rank] and partial_lse [splits, heads, tokens]
 // float; `tokens`: the step's token rows; `two_blocks`: the single-token form as two blocks of eight warps per SM).  error_flag (device int, zero; may be null): set to 31 if a wait for a
-// tile of entries ever gave up.
+// tile of entries ever gave up.  window > 0: a query sees the newest `window` keys up to its own; cos_sin_scale
+// multiplies every cosine and sine of the query's rotation.
 LI_EXPORT int li_latent_attention_mma(const void* q_lat, long q_lat_head_stride, int q_lat_token_stride,
                                       const void* q_raw, int q_raw_token_stride, int q_raw_head_stride, int q_rot_off,
                                       void* out, long out_head_stride, int out_token_stride, const void* pool,
@@ -604,7 +609,8 @@ LI_EXPORT int li_latent_attention_mma(const void* q_lat, long q_lat_head_stride,
                                       const float* sink, int num_seqs, int max_q_len, int heads, int kv_rank,
                                       int rot_dim, int rot_dims, int page_size, int num_pages, float scale,
                                       int num_splits, float* partial_out, float* partial_lse, int tokens,
-                                      int two_blocks, int* error_flag, cudaStream_t stream) {
+                                      int two_blocks, int* error_flag, int window, float cos_sin_scale,
+                                      cudaStream_t stream) {
   if (num_seqs == 0 || max_q_len == 0) return 0;
   if (!li_latent_attention_mma_supports(kv_rank, rot_dim, rot_dims) || num_seqs > 65535) return LI_ERR_UNSUPPORTED;
   if (!aligned16(q_lat) || !aligned16(pool) || (q_lat_token_stride % 8) || (q_lat_head_stride % 8) || (out_token_stride % 2) ||
@@ -623,6 +629,7 @@ LI_EXPORT int li_latent_attention_mma(const void* q_lat, long q_lat_head_stride,
   p.inv_freq = inv_freq; p.sink = sink; p.heads = heads; p.rot_dims = rot_dims; p.page_size = page_size;
   p.num_pages = num_pages; p.scale_log2 = scale * kLog2e; p.num_splits = num_splits < 1 ? 1 : num_splits;
   p.partial_out = partial_out; p.partial_lse = partial_lse; p.tokens = tokens; p.error_flag = error_flag;
+  p.window = window; p.cs_scale = cos_sin_scale;
   int code;
   if (kv_rank == 64) code = launch_latent_sizes<64, 32>(p, num_seqs, max_q_len, two_blocks, stream);
   else if (kv_rank == 128 && rot_dim == 32) code = launch_latent_sizes<128, 32>(p, num_seqs, max_q_len, two_blocks, stream);

@@ -380,6 +380,7 @@ attention_mma_kernel(const AttnParams p) {
       const int row = row_base + g + 8 * h;
       if (row >= rows_used) continue;
       const int qi = q0 + row / groups, head = kvh * groups + row % groups;
+      if (p.num_splits == 1 && p.sink != nullptr) l[h] += exp2f(p.sink[head] * kLog2e - m[h]);
       const float inv = l[h] > 0.f ? 1.f / l[h] : 0.f;
       if (p.num_splits == 1) {
         bf16* dst = p.out + (size_t)(q_begin + qi) * p.out_row_stride + (size_t)head * D;
@@ -457,7 +458,8 @@ LI_EXPORT int li_paged_attention_mma_decode_capacity(int head_dim) {
 
 // Tensor-core paged attention (bfloat16; head_dim 64 or 128; groups of at most 64 heads).
 // keep_first (with a window): the first keys of a sequence stay visible behind the window.  softcap > 0: a scaled
-// score s becomes softcap * tanh(s / softcap).  Neither goes with rope_inv_freq.
+// score s becomes softcap * tanh(s / softcap).  Neither goes with rope_inv_freq.  sink (optional, [heads] float32):
+// exp(sink[h]) is one more term of head h's denominator.
 // seq_index (optional, [num_seqs]): the batch rows to run, so that a mixed step can send its
 // single-token sequences through a split launch and the others through an unsplit one.
 // num_splits > 1 needs scratch: partial_out [tokens*heads*splits, head_dim] and partial_lse
@@ -476,7 +478,7 @@ LI_EXPORT int li_paged_attention_mma(const void* q, int q_row_stride, void* out,
                                      int head_dim, int page_size, int num_pages, float scale, int window,
                                      int num_splits, float* partial_out, float* partial_lse, unsigned* counters,
                                      const float* rope_inv_freq, const void* k_new, const void* v_new, int store_new,
-                                     int keep_first, float softcap, cudaStream_t stream) {
+                                     int keep_first, float softcap, const float* sink, cudaStream_t stream) {
   if (num_seqs == 0 || max_q_len == 0) return 0;
   if (rope_inv_freq && (keep_first > 0 || softcap > 0.f)) return LI_ERR_UNSUPPORTED;
   if (scale == 0.f) return LI_ERR_UNSUPPORTED;
@@ -498,6 +500,7 @@ LI_EXPORT int li_paged_attention_mma(const void* q, int q_row_stride, void* out,
   p.keep_first = window > 0 && keep_first > 0 ? keep_first : 0;
   p.cap_in = softcap > 0.f ? scale / softcap : 0.f;
   p.cap_out = softcap > 0.f ? softcap / scale : 0.f;
+  p.sink = sink;
   const bool decode = max_q_len == 1 && groups <= 16;
   if (rope_inv_freq && (!decode || !k_new || !v_new || !aligned16(k_new) || !aligned16(v_new))) return LI_ERR_UNSUPPORTED;
   if (!decode)

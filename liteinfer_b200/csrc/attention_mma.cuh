@@ -44,6 +44,9 @@ struct AttnParams {
   // cap_in = scale / cap, cap_out = cap / scale.
   int keep_first;
   float cap_in, cap_out;
+  // [heads] float or null: exp(sink[h]) is one more term of head h's denominator, with no key and no value.  It is
+  // added where a row's final result is made (the unsplit epilogues, or the merge of the splits), exactly once.
+  const float* sink;
 };
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
@@ -112,6 +115,7 @@ __device__ __forceinline__ void combine_warps(const AttnParams& p, const float* 
       acc += wgt * os[((size_t)w * 16 + row) * D + d];
     }
     const int qi = q0 + row / groups, head = kvh * groups + row % groups;
+    if (p.num_splits == 1 && p.sink != nullptr) denom += exp2f(p.sink[head] * kLog2e - mx);
     const float value = denom > 0.f ? acc / denom : 0.f;
     if (p.num_splits == 1) {
       p.out[(size_t)(q_begin + qi) * p.out_row_stride + (size_t)head * D + d] = __float2bfloat16_rn(value);
@@ -198,6 +202,7 @@ __device__ __forceinline__ void merge_splits(const AttnParams& p, unsigned char*
       mx = top;
     }
     if (live && part == 0) {
+      if (p.sink != nullptr) denom += exp2f(p.sink[head] * kLog2e - mx);
       const float inv = denom > 0.f ? 1.f / denom : 0.f;
       bf16* dst = p.out + (size_t)(q_begin + qi) * p.out_row_stride + (size_t)head * D + d4 * 4;
       *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc.x * inv, acc.y * inv), pack_bf16(acc.z * inv, acc.w * inv));

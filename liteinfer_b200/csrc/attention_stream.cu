@@ -605,6 +605,7 @@ LI_EXPORT int li_paged_attention_stream_capacity(int head_dim) {
 // Every launched sequence brings exactly one token.  Arguments as li_paged_attention_mma (its counters export
 // says how many counters a split launch needs); sizes as li_paged_attention_stream_supports allows.
 // error_flag (device int, zero; may be null): set to 21 if a wait for a group of keys ever gave up.
+// sink (optional, [heads] float32): exp(sink[h]) is one more term of head h's denominator.
 LI_EXPORT int li_paged_attention_stream(const void* q, int q_row_stride, void* out, int out_row_stride,
                                         const void* k_pool, const void* v_pool, const int* block_table,
                                         int table_stride, const int* query_start_loc, const int* context_lens,
@@ -612,7 +613,7 @@ LI_EXPORT int li_paged_attention_stream(const void* q, int q_row_stride, void* o
                                         int page_size, int num_pages, float scale, int window, int num_splits,
                                         float* partial_out, float* partial_lse, unsigned* counters,
                                         const float* rope_inv_freq, const void* k_new, const void* v_new,
-                                        int store_new, int* error_flag, cudaStream_t stream) {
+                                        int store_new, int* error_flag, const float* sink, cudaStream_t stream) {
   if (num_seqs == 0) return 0;
   if (!li_paged_attention_stream_supports(heads, kv_heads, head_dim, page_size)) return LI_ERR_UNSUPPORTED;
   if (kv_heads > 65535 || num_seqs > 65535 || num_splits < 1 || num_splits > 32) return LI_ERR_UNSUPPORTED;
@@ -636,7 +637,8 @@ LI_EXPORT int li_paged_attention_stream(const void* q, int q_row_stride, void* o
   // while the one before it drains (programmatic dependent launch), a launch of clusters starts later than a
   // launch of single blocks does, and the step loses more than the merge gains (1.065 against 0.948 ms).
   const char* cluster_env = getenv("LITEINFER_ATTN_CLUSTER_MERGE");
-  if (cluster_env && atoi(cluster_env) == 1 && num_splits >= 2 && num_splits <= 16 &&
+  p.sink = sink;      // added by the merges of attention_mma.cuh; the merge inside a cluster does not know it
+  if (cluster_env && atoi(cluster_env) == 1 && sink == nullptr && num_splits >= 2 && num_splits <= 16 &&
       li_paged_attention_stream_cluster_capacity(head_dim, num_splits) >= kv_heads * num_seqs)
     p.cluster_merge = 1;
   if ((page_size & (page_size - 1)) == 0)

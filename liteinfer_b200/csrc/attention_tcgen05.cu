@@ -79,6 +79,7 @@ struct TcAttnParams {
   // s becomes cap_out * tanh(s * cap_in) and is then scaled like any other (cap_in = scale / cap, cap_out = cap / scale).
   int keep_first;
   float cap_in, cap_out;
+  const float* sink;      // [heads] float or null: exp(sink[h]) is one more term of head h's denominator (no key, no value)
 };
 
 // tanh(x) = 1 - 2 / (1 + e^(2x)) from one exponential and one division; exact at both ends, a few 1e-7 between.
@@ -451,8 +452,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
     // Output: wait for the last P V, read the row, divide by the row's sum, store.
     if (ok && ntiles > 0 && mbar_wait(pv_done((ntiles - 1) & 1), (unsigned)((ntiles - 1) >> 1) & 1, p.error_flag, 19)) {
       tcgen05_fence_after();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
       const int qi = q0 + row / groups, head = kvh * groups + row % groups;
+      // The exponentials were taken against m (unscaled), so the sink's term is too.
+      if (p.sink != nullptr && row < rows_used) l += exp2f(p.sink[head] * kLog2eF - m * p.scale_log2);
+      const float inv = l > 0.f ? 1.f / l : 0.f;
       bf16* dst = p.out + (size_t)(q_begin + qi) * p.out_row_stride + (size_t)head * D;
 #pragma unroll
       for (int half = 0; half < D / 32; ++half) {
@@ -558,7 +561,8 @@ LI_EXPORT int li_paged_attention_tcgen05(const void* q, int q_row_stride, void* 
                                          int table_stride, const int* query_start_loc, const int* context_lens,
                                          const int* seq_index, int num_seqs, int max_q_len, int heads, int kv_heads,
                                          int head_dim, int page_size, int num_pages, float scale, int window,
-                                         int* error_flag, int keep_first, float softcap, cudaStream_t stream) {
+                                         int* error_flag, int keep_first, float softcap, const float* sink,
+                                         cudaStream_t stream) {
   if (num_seqs == 0 || max_q_len == 0) return 0;
   if (softcap > 0.f && scale == 0.f) return LI_ERR_UNSUPPORTED;
   if (!li_paged_attention_tcgen05_supports(heads, kv_heads, head_dim, page_size)) return LI_ERR_UNSUPPORTED;
@@ -575,7 +579,7 @@ LI_EXPORT int li_paged_attention_tcgen05(const void* q, int q_row_stride, void* 
   TcAttnParams p{(const bf16*)q, q_row_stride, (bf16*)out, out_row_stride, block_table, table_stride,
                  query_start_loc, context_lens, seq_index, heads, kv_heads, page_size, shift, num_pages,
                  scale * kLog2eF, window, error_flag, window > 0 && keep_first > 0 ? keep_first : 0,
-                 softcap > 0.f ? scale / softcap : 0.f, softcap > 0.f ? softcap / scale : 0.f};
+                 softcap > 0.f ? scale / softcap : 0.f, softcap > 0.f ? softcap / scale : 0.f, sink};
   const int groups = heads / kv_heads;
   const int tq = kRows / groups;
   // Two query tiles per block at head size 128 where some sequence brings enough queries for two

@@ -178,6 +178,15 @@ __global__ void activation_kernel(const T* __restrict__ x, T* __restrict__ out, 
     out[i] = from_float<T>(activate(to_float(x[i]), act));
 }
 
+// x <- cap * tanh(x / cap) in place (32-bit inside): the soft cap of a model's logits.
+template <typename T>
+__global__ void softcap_kernel(T* __restrict__ x, size_t n, float cap, float inv_cap) {
+  grid_dependency_wait();
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += stride)
+    x[i] = from_float<T>(cap * tanhf(to_float(x[i]) * inv_cap));
+}
+
 // gate_up [rows, 2*width]: gate in the first `width` columns, up in the rest.
 template <typename T>
 __global__ void act_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, size_t rows, int width, int act) {
@@ -416,5 +425,17 @@ LI_EXPORT int li_activation(int dtype, const void* x, void* out, size_t n, int a
     e = launch_pdl((long)n, activation_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)x, (float*)out, n, act);
   else
     e = launch_pdl((long)n, activation_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (const bf16*)x, (bf16*)out, n, act);
+  return (int)e;
+}
+
+LI_EXPORT int li_softcap(int dtype, void* x, size_t n, float cap, cudaStream_t stream) {
+  if (n == 0) return 0;
+  if (!(cap > 0.f)) return LI_ERR_UNSUPPORTED;
+  const int blocks = (int)(n / 256 + 1 < 148 * 8 ? n / 256 + 1 : 148 * 8);
+  cudaError_t e;
+  if (dtype == kFloat32)
+    e = launch_pdl((long)n, softcap_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)x, n, cap, 1.0f / cap);
+  else
+    e = launch_pdl((long)n, softcap_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (bf16*)x, n, cap, 1.0f / cap);
   return (int)e;
 }

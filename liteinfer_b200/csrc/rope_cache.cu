@@ -24,7 +24,11 @@
 // The row may be wider than q, k and v (further columns of a fused projection follow them).  Statistics, the
 // blend and the rotation are 32-bit; each result is rounded once.
 //
-// li_sigmoid_gate_heads multiplies head h of every row of x by sigmoid(gate[row, h]) in place.
+// `norm_flags`: bit 0, q and k are divided by their root mean square also where no weight is given; bit 1, the norm
+// (and its weight) comes behind the rotation instead of in front of it.
+//
+// li_sigmoid_gate_heads multiplies head h of every row of x by sigmoid(gate[row, h]) in place; li_sigmoid_gate
+// every element by the sigmoid of its own gate.
 #include "common.cuh"
 
 namespace li {
@@ -40,8 +44,9 @@ head_norm_rope_kv_write_kernel(T* __restrict__ qkv, size_t row_stride, const int
                                int rotary_dim, int page_size, int num_pages, int v_dim,
                                const T* __restrict__ q_norm, const T* __restrict__ k_norm, float norm_eps,
                                const T* __restrict__ v_other, size_t v_other_stride,
-                               const float* __restrict__ lambda) {
+                               const float* __restrict__ lambda, int norm_flags) {
   extern __shared__ float shared[];  // cos[half], sin[half], then one head per warp
+  const bool unit = norm_flags & 1, after = norm_flags & 2;
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   grid_launch_dependents();
@@ -74,19 +79,27 @@ head_norm_rope_kv_write_kernel(T* __restrict__ qkv, size_t row_stride, const int
       head[j] = x;
       ss = fmaf(x, x, ss);
     }
-    if (w != nullptr) {
+    const bool normed = w != nullptr || unit;
+    if (normed && !after) {
       const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)head_dim + norm_eps);
-      for (int j = lane; j < head_dim; j += 32) head[j] = head[j] * inv * to_float(w[j]);
+      for (int j = lane; j < head_dim; j += 32) head[j] = head[j] * inv * (w != nullptr ? to_float(w[j]) : 1.0f);
     }
     __syncwarp();
     T* dst = is_q ? p : k_pool + (((size_t)page * kv_heads + (h - heads)) * page_size + slot) * head_dim;
     if (is_q || store) {
-      for (int j = lane; j < head_dim; j += 32) {
-        float r;
-        if (j < half) r = rotate_lo(head[j], head[j + half], cosv[j], sinv[j]);
-        else if (j < rotary_dim) r = rotate_hi(head[j - half], head[j], cosv[j - half], sinv[j - half]);
-        else r = head[j];
-        dst[j] = from_float<T>(r);
+      // With the norm behind the rotation the head is rotated twice: once for its sum of squares, once to be stored.
+      float inv = 1.0f;
+      for (int pass = (normed && after) ? 0 : 1; pass < 2; ++pass) {
+        float ss2 = 0.f;
+        for (int j = lane; j < head_dim; j += 32) {
+          float r;
+          if (j < half) r = rotate_lo(head[j], head[j + half], cosv[j], sinv[j]);
+          else if (j < rotary_dim) r = rotate_hi(head[j - half], head[j], cosv[j - half], sinv[j - half]);
+          else r = head[j];
+          if (pass == 0) ss2 = fmaf(r, r, ss2);
+          else dst[j] = from_float<T>((normed && after) ? r * inv * (w != nullptr ? to_float(w[j]) : 1.0f) : r);
+        }
+        if (pass == 0) inv = 1.0f / sqrtf(warp_sum(ss2) / (float)head_dim + norm_eps);
       }
     }
     __syncwarp();
@@ -115,9 +128,10 @@ head_norm_rope_kv_write_vec_kernel(T* __restrict__ qkv, size_t row_stride, const
                                    int rotary_dim, int page_size, int num_pages, int v_dim,
                                    const T* __restrict__ q_norm, const T* __restrict__ k_norm, float norm_eps,
                                    const T* __restrict__ v_other, size_t v_other_stride,
-                                   const float* __restrict__ lambda, int group_shift) {
+                                   const float* __restrict__ lambda, int group_shift, int norm_flags) {
   constexpr int N = Vec16<T>::N;
   extern __shared__ float shared[];  // cos[half], sin[half]
+  const bool unit = norm_flags & 1, after = norm_flags & 2;
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31;
   grid_launch_dependents();
@@ -157,10 +171,13 @@ head_norm_rope_kv_write_vec_kernel(T* __restrict__ qkv, size_t row_stride, const
 #pragma unroll
     for (int e = 0; e < N; ++e) ss = fmaf(x[e], x[e], ss);
     for (int o = group >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);   // by every lane of the warp
-    if (w != nullptr) {
+    const bool normed = w != nullptr || unit;
+    float wv[N];
+#pragma unroll
+    for (int e = 0; e < N; ++e) wv[e] = 1.0f;
+    if (w != nullptr) unpack16(load16(w + j0), wv);
+    if (normed && !after) {
       const float inv = 1.0f / sqrtf(ss / (float)head_dim + norm_eps);
-      float wv[N];
-      unpack16(load16(w + j0), wv);
 #pragma unroll
       for (int e = 0; e < N; ++e) x[e] = x[e] * inv * wv[e];
     }
@@ -184,11 +201,23 @@ head_norm_rope_kv_write_vec_kernel(T* __restrict__ qkv, size_t row_stride, const
       for (int e = 0; e < N; ++e) { c[e] = 1.0f; sn[e] = 0.f; }
     }
     Vec16<T> result;
+    float r[N];
 #pragma unroll
     for (int e = 0; e < N; ++e) {
       const float y = __shfl_sync(0xffffffffu, x[e], from);
-      result.set(e, j0 < rotary_dim ? __fadd_rn(__fmul_rn(x[e], c[e]), __fmul_rn(y, sn[e])) : x[e]);
+      r[e] = j0 < rotary_dim ? __fadd_rn(__fmul_rn(x[e], c[e]), __fmul_rn(y, sn[e])) : x[e];
     }
+    if (normed && after) {        // the norm behind the rotation: the root mean square of what was rotated
+      float ss2 = 0.f;
+#pragma unroll
+      for (int e = 0; e < N; ++e) ss2 = fmaf(r[e], r[e], ss2);
+      for (int o = group >> 1; o > 0; o >>= 1) ss2 += __shfl_xor_sync(0xffffffffu, ss2, o);
+      const float inv = 1.0f / sqrtf(ss2 / (float)head_dim + norm_eps);
+#pragma unroll
+      for (int e = 0; e < N; ++e) r[e] = r[e] * inv * wv[e];
+    }
+#pragma unroll
+    for (int e = 0; e < N; ++e) result.set(e, r[e]);
     if (active && (is_q || store)) {
       T* dst = is_q ? p : k_pool + (((size_t)page * kv_heads + (h - heads)) * page_size + slot) * head_dim + j0;
       store16(dst, result);
@@ -241,6 +270,30 @@ __global__ void sigmoid_gate_heads_kernel(T* __restrict__ x, const T* __restrict
     const int h = (int)((i - t * width) / size);
     const float g = to_float(gate[t * gate_stride + h]);
     x[i] = from_float<T>(to_float(x[i]) * (1.0f / (1.0f + expf(-g))));
+  }
+}
+
+// x [tokens, width] *= sigmoid(gate [tokens, width]) element by element; the vector form reads 16 bytes of each.
+template <typename T, bool kVec>
+__global__ void sigmoid_gate_kernel(T* __restrict__ x, const T* __restrict__ gate, size_t gate_stride, size_t tokens,
+                                    int width) {
+  constexpr int N = kVec ? Vec16<T>::N : 1;
+  grid_dependency_wait();
+  const size_t per_row = (size_t)width / N, total = tokens * per_row;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / per_row, c = (i - t * per_row) * N;
+    if (kVec) {
+      Vec16<T> v = load16(x + t * width + c);
+      float a[Vec16<T>::N], g[Vec16<T>::N];
+      unpack16(v, a);
+      unpack16(load16(gate + t * gate_stride + c), g);
+#pragma unroll
+      for (int e = 0; e < Vec16<T>::N; ++e) v.set(e, a[e] * (1.0f / (1.0f + expf(-g[e]))));
+      store16(x + t * width + c, v);
+    } else {
+      const float g = to_float(gate[t * gate_stride + c]);
+      x[t * width + c] = from_float<T>(to_float(x[t * width + c]) * (1.0f / (1.0f + expf(-g))));
+    }
   }
 }
 
@@ -400,7 +453,7 @@ LI_EXPORT int li_head_norm_rope_kv_write(int dtype, void* qkv, size_t row_stride
                                          int kv_heads, int head_dim, int rotary_dim, int page_size, int num_pages,
                                          int v_dim, const void* q_norm, const void* k_norm, float norm_eps,
                                          const void* v_other, size_t v_other_stride, const float* lambda,
-                                         cudaStream_t stream) {
+                                         int norm_flags, cudaStream_t stream) {
   if (tokens == 0) return 0;
   if (v_dim < 1 || head_dim < 1) return LI_ERR_UNSUPPORTED;
   if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return LI_ERR_UNSUPPORTED;
@@ -425,12 +478,12 @@ LI_EXPORT int li_head_norm_rope_kv_write(int dtype, void* qkv, size_t row_stride
                                stream, (float*)qkv, row_stride, positions, seq_of_token, block_table, table_stride,
                                (float*)k_pool, (float*)v_pool, inv_freq, heads, kv_heads, head_dim, rotary_dim,
                                page_size, num_pages, v_dim, (const float*)q_norm, (const float*)k_norm, norm_eps,
-                               (const float*)v_other, v_other_stride, lambda, shift);
+                               (const float*)v_other, v_other_stride, lambda, shift, norm_flags);
       return (int)launch_pdl(tokens, head_norm_rope_kv_write_vec_kernel<bf16>, dim3(tokens), dim3(kPrepWarps * 32), cs,
                              stream, (bf16*)qkv, row_stride, positions, seq_of_token, block_table, table_stride,
                              (bf16*)k_pool, (bf16*)v_pool, inv_freq, heads, kv_heads, head_dim, rotary_dim, page_size,
                              num_pages, v_dim, (const bf16*)q_norm, (const bf16*)k_norm, norm_eps,
-                             (const bf16*)v_other, v_other_stride, lambda, shift);
+                             (const bf16*)v_other, v_other_stride, lambda, shift, norm_flags);
     }
   }
   const size_t smem = ((size_t)rotary_dim + (size_t)kPrepWarps * head_dim) * sizeof(float);
@@ -440,12 +493,12 @@ LI_EXPORT int li_head_norm_rope_kv_write(int dtype, void* qkv, size_t row_stride
                            stream, (float*)qkv, row_stride, positions, seq_of_token, block_table, table_stride,
                            (float*)k_pool, (float*)v_pool, inv_freq, heads, kv_heads, head_dim, rotary_dim, page_size,
                            num_pages, v_dim, (const float*)q_norm, (const float*)k_norm, norm_eps,
-                           (const float*)v_other, v_other_stride, lambda);
+                           (const float*)v_other, v_other_stride, lambda, norm_flags);
   return (int)launch_pdl(tokens, head_norm_rope_kv_write_kernel<bf16>, dim3(tokens), dim3(kPrepWarps * 32), smem, stream,
                          (bf16*)qkv, row_stride, positions, seq_of_token, block_table, table_stride, (bf16*)k_pool,
                          (bf16*)v_pool, inv_freq, heads, kv_heads, head_dim, rotary_dim, page_size, num_pages, v_dim,
                          (const bf16*)q_norm, (const bf16*)k_norm, norm_eps, (const bf16*)v_other, v_other_stride,
-                         lambda);
+                         lambda, norm_flags);
 }
 
 LI_EXPORT int li_sigmoid_gate_heads(int dtype, void* x, const void* gate, size_t gate_stride, int tokens, int heads,
@@ -469,4 +522,21 @@ LI_EXPORT int li_sigmoid_gate_heads(int dtype, void* x, const void* gate, size_t
                            (const float*)gate, gate_stride, (size_t)tokens, heads, size);
   return (int)launch_pdl(tokens, sigmoid_gate_heads_kernel<bf16>, grid, dim3(256), 0, stream, (bf16*)x,
                          (const bf16*)gate, gate_stride, (size_t)tokens, heads, size);
+}
+
+// x [tokens, width] (contiguous) *= sigmoid(gate [tokens, width]) (rows gate_stride apart), in place; 32-bit inside.
+LI_EXPORT int li_sigmoid_gate(int dtype, void* x, const void* gate, size_t gate_stride, int tokens, int width,
+                              cudaStream_t stream) {
+  if (tokens <= 0 || width <= 0) return 0;
+  const int n = dtype == kFloat32 ? 4 : 8;
+  const bool vec = width % n == 0 && gate_stride % n == 0 && aligned16(x) && aligned16(gate);
+  const size_t total = (size_t)tokens * width / (vec ? n : 1);
+  const dim3 grid((unsigned)((total + 255) / 256 < 8192 ? (total + 255) / 256 : 8192));
+#define LI_GATE(T, V)                                                                                              \
+  return (int)launch_pdl(tokens, sigmoid_gate_kernel<T, V>, grid, dim3(256), 0, stream, (T*)x, (const T*)gate,     \
+                         gate_stride, (size_t)tokens, width)
+  if (dtype == kFloat32) { if (vec) LI_GATE(float, true); LI_GATE(float, false); }
+  if (vec) LI_GATE(bf16, true);
+  LI_GATE(bf16, false);
+#undef LI_GATE
 }

@@ -50,14 +50,23 @@ _SIGNATURES = {
     "li_head_norm_rope_kv_write": ("rope_cache", [c_int, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p, c_int,
                                                   c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                                   c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p,
-                                                  c_size_t, c_void_p, c_void_p]),
+                                                  c_size_t, c_void_p, c_int, c_void_p]),
+    "li_sigmoid_gate": ("rope_cache", [c_int, c_void_p, c_void_p, c_size_t, c_int, c_int, c_void_p]),
+    "li_softcap": ("elementwise", [c_int, c_void_p, c_size_t, c_float, c_void_p]),
+    "li_moe_route": ("moe", [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "li_moe_tile_rows": ("moe", [c_int, c_int, c_int]),
+    "li_moe_sort": ("moe", [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+    "li_moe_grouped": ("moe", [c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p,
+                               c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_int,
+                               c_int, c_void_p]),
+    "li_moe_combine": ("moe", [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "li_sigmoid_gate_heads": ("rope_cache", [c_int, c_void_p, c_void_p, c_size_t, c_int, c_int, c_int, c_void_p]),
     "li_mlstm": ("mlstm", [c_int, c_void_p, c_size_t, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
                            c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
                            c_int, c_int, c_void_p]),
     "li_paged_attention_generic": ("attention_generic", [
         c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-        c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_float, c_void_p]),
+        c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_float, c_void_p, c_void_p]),
     "li_convert": ("layernorm", [c_int, c_void_p, c_size_t, c_int, c_void_p, c_size_t, c_int, c_int, c_void_p]),
     "li_layernorm": ("layernorm", [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                    c_int, c_int, c_float, c_float, c_int, c_int, c_void_p]),
@@ -75,11 +84,11 @@ _SIGNATURES = {
     "li_paged_attention_mma": ("attention_mma", [
         c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
         c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p,
-        c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p]),
+        c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p]),
     "li_paged_attention_stream": ("attention_stream", [
         c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
         c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p,
-        c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+        c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
     "li_paged_attention_stream_supports": ("attention_stream", [c_int, c_int, c_int, c_int]),
     "li_paged_attention_stream_capacity": ("attention_stream", [c_int]),
     "li_paged_attention_stream_cluster_capacity": ("attention_stream", [c_int, c_int]),
@@ -87,7 +96,7 @@ _SIGNATURES = {
     "li_paged_attention_mma_decode_capacity": ("attention_mma", [c_int]),
     "li_paged_attention_tcgen05": ("attention_tcgen05", [
         c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-        c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_float, c_void_p]),
+        c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_int, c_float, c_void_p, c_void_p]),
     "li_paged_attention_tcgen05_supports": ("attention_tcgen05", [c_int, c_int, c_int, c_int]),
     "li_gemm_skinny": ("gemm_skinny", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                        c_void_p, c_size_t, c_void_p, c_int, c_void_p]),
@@ -110,15 +119,15 @@ _SIGNATURES = {
                                          c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p]),
     "li_latent_prep": ("attention_latent", [c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                             c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
-                                            c_int, c_int, c_void_p, c_int, c_void_p]),
+                                            c_int, c_int, c_void_p, c_int, c_float, c_void_p]),
     "li_latent_attention": ("attention_latent", [c_int, c_void_p, c_long, c_int, c_void_p, c_int, c_int, c_int,
                                                  c_void_p, c_long, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                                  c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                                 c_int, c_float, c_void_p]),
+                                                 c_int, c_float, c_int, c_float, c_void_p]),
     "li_latent_attention_mma": ("attention_latent_mma", [
         c_void_p, c_long, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_long, c_int, c_void_p, c_void_p, c_int,
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-        c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
+        c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_float, c_void_p]),
     "li_latent_attention_mma_supports": ("attention_latent_mma", [c_int, c_int, c_int]),
     "li_gate_heads": ("attention_latent", [c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]),
     "li_argmax": ("sampling", [c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
@@ -685,7 +694,8 @@ def head_norm_rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, seq_of_t
                             inv_freq: torch.Tensor | None, heads: int, kv_heads: int, head_dim: int, rotary_dim: int,
                             q_norm: torch.Tensor | None, k_norm: torch.Tensor | None, norm_eps: float,
                             store: bool = True, v_other: torch.Tensor | None = None,
-                            blend: torch.Tensor | None = None) -> None:
+                            blend: torch.Tensor | None = None, unit_norm: bool = False,
+                            norm_after_rotation: bool = False) -> None:
     """`rope_kv_write` for an attention whose q and k pass a root-mean-square norm per head first: every q head
     becomes rot(q_norm * q / sqrt(mean(q^2) + eps)) in place, every k head likewise (with k_norm) on its way into
     its page; None leaves that projection unnormalised.  q_norm and k_norm: [head_dim], the dtype of qkv.
@@ -693,7 +703,9 @@ def head_norm_rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, seq_of_t
     qkv [tokens, >= (heads + kv_heads) * head_dim + kv_heads * v_dim]: q, k, v side by side at the start of each
     row (further columns may follow; v_dim is the value pool's last axis).  `v_other` [tokens, kv_heads * v_dim]
     (a column slice is fine) with `blend` (one float32 on the device): what is stored is
-    (1 - blend) * v + blend * v_other, computed in 32-bit and rounded once."""
+    (1 - blend) * v + blend * v_other, computed in 32-bit and rounded once.  `unit_norm`: q and k are divided by
+    their root mean square per head also where no weight is given.  `norm_after_rotation`: the norm (of the rotated
+    head, with its weight if any) comes behind the rotation instead of in front of it."""
     _rows2d(qkv, "qkv")
     _on_gpu(positions, seq_of_token, block_table, k_pool, v_pool, inv_freq, q_norm, k_norm, blend)
     _int32(positions, "positions"); _int32(seq_of_token, "seq_of_token"); _int32(block_table, "block_table")
@@ -716,7 +728,26 @@ def head_norm_rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, seq_of_t
         block_table.data_ptr(), block_table.stride(0), k_pool.data_ptr(), v_pool.data_ptr(), _ptr(inv_freq), tokens,
         heads, kv_heads, head_dim, rotary_dim if inv_freq is not None else 0, page_size, pages if store else 0, vd,
         _ptr(q_norm), _ptr(k_norm), float(norm_eps), _ptr(v_other), v_other.stride(0) if v_other is not None else 0,
-        _ptr(blend), _stream()), "head_norm_rope_kv_write")
+        _ptr(blend), int(unit_norm) | (2 if norm_after_rotation else 0), _stream()), "head_norm_rope_kv_write")
+
+
+def sigmoid_gate_(x: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """x[t, j] *= sigmoid(gate[t, j]) in place, element by element: x [tokens, width] contiguous, gate [tokens,
+    width] (a column slice is fine), both in the engine's dtype; the sigmoid and the product are 32-bit."""
+    _on_gpu(x)
+    _rows2d(gate, "gate")
+    assert gate.shape == x.shape and gate.dtype == x.dtype and x.is_contiguous()
+    _check(_fn("li_sigmoid_gate")(_code(x), x.data_ptr(), gate.data_ptr(), gate.stride(0), x.shape[0], x.shape[1],
+                                  _stream()), "sigmoid_gate")
+    return x
+
+
+def softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """x <- cap * tanh(x / cap) in place (32-bit inside)."""
+    _on_gpu(x)
+    assert x.is_contiguous() and cap > 0
+    _check(_fn("li_softcap")(_code(x), x.data_ptr(), x.numel(), float(cap), _stream()), "softcap")
+    return x
 
 
 def sigmoid_gate_heads_(x: torch.Tensor, gate: torch.Tensor, heads: int) -> torch.Tensor:
@@ -788,30 +819,32 @@ def cluster_capacity(head_dim: int, splits: int) -> int:
 
 def paged_attention_generic(q, q_row_stride, out, k_pool, v_pool, block_table, query_start_loc, context_lens,
                             num_seqs, max_q_len, heads, kv_heads, head_dim, scale, window=0, keep_first=0,
-                            softcap=0.0) -> torch.Tensor:
+                            softcap=0.0, sink=None) -> torch.Tensor:
     """The plain SIMT kernel: any dtype, key and value sizes up to 256 (they may differ), any grouping, a window
-    that may keep the first `keep_first` keys visible, scores capped by softcap * tanh(score / softcap)."""
-    _on_gpu(q, out, k_pool, v_pool, block_table, query_start_loc, context_lens)
+    that may keep the first `keep_first` keys visible, scores capped by softcap * tanh(score / softcap), a sink."""
+    _on_gpu(q, out, k_pool, v_pool, block_table, query_start_loc, context_lens, sink)
     pages, kvh, page_size, hd = k_pool.shape
     _check(_fn("li_paged_attention_generic")(
         _code(q), q.data_ptr(), q_row_stride, out.data_ptr(), out.stride(0), k_pool.data_ptr(), v_pool.data_ptr(),
         block_table.data_ptr(), block_table.stride(0), query_start_loc.data_ptr(), context_lens.data_ptr(),
         num_seqs, max_q_len, heads, kv_heads, head_dim, v_pool.shape[3], page_size, pages, float(scale), int(window),
-        int(keep_first), float(softcap), _stream()),
+        int(keep_first), float(softcap), _ptr(sink), _stream()),
         "paged_attention_generic")
     return out
 
 
 def paged_attention_mma(q, q_row_stride, out, k_pool, v_pool, block_table, query_start_loc, context_lens,
                         seq_index, num_seqs, max_q_len, heads, kv_heads, head_dim, scale, window=0,
-                        num_splits=1, newest=None, streaming=False, keep_first=0, softcap=0.0) -> torch.Tensor:
+                        num_splits=1, newest=None, streaming=False, keep_first=0, softcap=0.0,
+                        sink=None) -> torch.Tensor:
     """The tensor-core kernel (bfloat16, head size 64 or 128); `num_splits` > 1 splits every sequence's keys
     over that many blocks, the last of which merges the partial results.  `newest` (NewestToken, single-token
     sequences only): q is unrotated and the newest key and value are not in their pages yet; the kernel
     rotates q and the key and stores key and value itself.  `streaming` (single-token sequences, sizes that
     `stream_attention_supports` allows): the kernel that passes K and V through registers only.  `keep_first`
-    (with a window) and `softcap`: as in `paged_attention`; not with `newest` or `streaming`."""
-    _on_gpu(q, out, k_pool, v_pool, block_table, query_start_loc, context_lens, seq_index)
+    (with a window) and `softcap`: as in `paged_attention`; not with `newest` or `streaming`.  `sink`: as in
+    `paged_attention`; every form takes it."""
+    _on_gpu(q, out, k_pool, v_pool, block_table, query_start_loc, context_lens, seq_index, sink)
     pages, kvh, page_size, hd = k_pool.shape
     partial_out = partial_lse = counters = None
     if num_splits > 1:
@@ -831,14 +864,14 @@ def paged_attention_mma(q, q_row_stride, out, k_pool, v_pool, block_table, query
             block_table.data_ptr(), block_table.stride(0), query_start_loc.data_ptr(), context_lens.data_ptr(),
             _ptr(seq_index), num_seqs, heads, kv_heads, head_dim, page_size, pages, float(scale), int(window),
             int(num_splits), _ptr(partial_out), _ptr(partial_lse), _ptr(counters), *tail,
-            scratch_for(q.device).gemm_error.data_ptr(), _stream()), "paged_attention_stream")
+            scratch_for(q.device).gemm_error.data_ptr(), _ptr(sink), _stream()), "paged_attention_stream")
         return out
     _check(_fn("li_paged_attention_mma")(
         q.data_ptr(), q_row_stride, out.data_ptr(), out.stride(0), k_pool.data_ptr(), v_pool.data_ptr(),
         block_table.data_ptr(), block_table.stride(0), query_start_loc.data_ptr(), context_lens.data_ptr(),
         _ptr(seq_index), num_seqs, max_q_len, heads, kv_heads, head_dim, page_size, pages, float(scale),
         int(window), int(num_splits), _ptr(partial_out), _ptr(partial_lse), _ptr(counters), *tail, int(keep_first),
-        float(softcap), _stream()),
+        float(softcap), _ptr(sink), _stream()),
         "paged_attention_mma")
     return out
 
@@ -862,17 +895,18 @@ def fused_decode_supports(dtype: torch.dtype, heads: int, kv_heads: int, head_di
 
 def paged_attention_tcgen05(q, q_row_stride, out, k_pool, v_pool, block_table, query_start_loc, context_lens,
                             seq_index, num_seqs, max_q_len, heads, kv_heads, head_dim, scale, window=0, keep_first=0,
-                            softcap=0.0) -> torch.Tensor:
+                            softcap=0.0, sink=None) -> torch.Tensor:
     """The tcgen05 / TMA / tensor-memory attention kernel for prompts and portions (bfloat16, head size 64 or 128,
     pages of 16, 32 or 64 tokens, groups of at most 128 heads; `keep_first` and `softcap` as in `paged_attention`).
     `gemm_error_flag(device)` tells afterwards whether a wait inside the kernel ever gave up."""
-    _on_gpu(q, out, k_pool, v_pool, block_table, query_start_loc, context_lens, seq_index)
+    _on_gpu(q, out, k_pool, v_pool, block_table, query_start_loc, context_lens, seq_index, sink)
     pages, kvh, page_size, hd = k_pool.shape
     _check(_fn("li_paged_attention_tcgen05")(
         q.data_ptr(), q_row_stride, out.data_ptr(), out.stride(0), k_pool.data_ptr(), v_pool.data_ptr(),
         block_table.data_ptr(), block_table.stride(0), query_start_loc.data_ptr(), context_lens.data_ptr(),
         _ptr(seq_index), num_seqs, max_q_len, heads, kv_heads, head_dim, page_size, pages, float(scale),
-        int(window), scratch_for(q.device).gemm_error.data_ptr(), int(keep_first), float(softcap), _stream()),
+        int(window), scratch_for(q.device).gemm_error.data_ptr(), int(keep_first), float(softcap), _ptr(sink),
+        _stream()),
         "paged_attention_tcgen05")
     return out
 
@@ -902,7 +936,7 @@ def paged_attention(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_poo
                     context_lens: torch.Tensor, num_seqs: int, max_q_len: int, heads: int, kv_heads: int,
                     head_dim: int, scale: float, window: int = 0, plan=None,
                     decode_splits: int | None = None, newest: "NewestToken | None" = None, keep_first: int = 0,
-                    softcap: float = 0.0) -> torch.Tensor:
+                    softcap: float = 0.0, sink: torch.Tensor | None = None) -> torch.Tensor:
     """Attention of each sequence's newest queries over its pages (any mix of portions and single tokens).
 
     q: the tensor holding the queries, head h of token t at q[t, h*head_dim:...]
@@ -914,7 +948,8 @@ def paged_attention(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_poo
     `newest`: only where `fused_decode_supports` said yes; see `paged_attention_mma`.
     `keep_first` (with a window): the first keys of a sequence stay visible behind the window.  `softcap` > 0:
     a scaled score s becomes softcap * tanh(s / softcap).  Values may have another size than keys
-    (`v_pool.shape[3]`); out is then [tokens, heads * value size].
+    (`v_pool.shape[3]`); out is then [tokens, heads * value size].  `sink` [heads] float32: exp(sink[h]) is one
+    more term of the denominator of head h's softmax; it has no key and no value and is not scaled.
     """
     _on_gpu(q, out, k_pool, v_pool, block_table, query_start_loc, context_lens)
     _int32(block_table, "block_table"); _int32(query_start_loc, "query_start_loc"); _int32(context_lens, "context_lens")
@@ -923,15 +958,18 @@ def paged_attention(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_poo
     if newest is not None and not fused_decode_supports(q.dtype, heads, kv_heads, head_dim, head_dim, plan):
         raise ValueError("the decode kernel with the rotary encoding fused in does not take this step")
     masked = softcap > 0 or (keep_first > 0 and window > 0)
+    assert sink is None or (sink.dtype == torch.float32 and sink.numel() == heads)
     if v_pool.shape[3] != head_dim or not mma_attention_supports(q.dtype, heads, kv_heads, head_dim):
         assert newest is None
         return paged_attention_generic(q, q_row_stride, out, k_pool, v_pool, block_table, query_start_loc,
                                        context_lens, num_seqs, max_q_len, heads, kv_heads, head_dim, scale, window,
-                                       keep_first, softcap)
+                                       keep_first, softcap, sink)
     common = (q, q_row_stride, out, k_pool, v_pool, block_table, query_start_loc, context_lens)
     # Kept first keys and capped scores are options of the tcgen05 kernel (prompts) and of the mma.sync kernel
     # (prompts it takes instead, and single tokens); the streaming decode kernel knows neither.
     options = dict(keep_first=keep_first, softcap=softcap) if masked else {}
+    if sink is not None:
+        options["sink"] = sink
     if plan is None:
         return paged_attention_mma(*common, None, num_seqs, max_q_len, heads, kv_heads, head_dim, scale, window,
                                    **options)
@@ -1296,39 +1334,47 @@ def batched_linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> 
 def latent_prep(proj: torch.Tensor, q_off: int, q_rank: int, kv_off: int | None, kv_rank: int, rot_dim: int,
                 rot_dims: int, q_weight: torch.Tensor, kv_weight: torch.Tensor | None, eps: float,
                 inv_freq: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
-                block_table: torch.Tensor, pool: torch.Tensor, q_out: torch.Tensor, store: bool = True) -> None:
+                block_table: torch.Tensor, pool: torch.Tensor, q_out: torch.Tensor | None, store: bool = True,
+                cos_sin_scale: float = 1.0) -> None:
     """Per token of `proj` [tokens, columns]: q_out = rmsnorm(proj[:, q_off:q_off + q_rank]) * q_weight, and, with
     `kv_off` and `store`, the token's cache entry pool[page, slot] = [rmsnorm(latent) * kv_weight | rotated key
     part], latent = proj[:, kv_off:kv_off + kv_rank], the key part the rot_dim columns behind it, of which the
     first `rot_dims` turn by position * inv_freq (pairs i, i + rot_dims / 2).  pool [pages, 1, page_size, kv_rank +
-    rot_dim]; norm weights float32; tokens whose sequence is -1 store nothing."""
+    rot_dim]; norm weights float32; tokens whose sequence is -1 store nothing.  `q_out` None (with `q_weight`
+    None): the layer has no query latent.  `cos_sin_scale` multiplies every cosine and sine."""
     _on_gpu(proj, q_weight, kv_weight, inv_freq, positions, seq_of_token, block_table, pool, q_out)
     _int32(positions, "positions"); _int32(seq_of_token, "seq_of_token"); _int32(block_table, "block_table")
     tokens = proj.shape[0]
     pages, one, page_size, entry = pool.shape
-    assert one == 1 and entry == kv_rank + rot_dim and pool.dtype == proj.dtype == q_out.dtype
-    assert q_out.shape == (tokens, q_rank) and q_weight.dtype == torch.float32 and q_weight.numel() == q_rank
+    assert one == 1 and entry == kv_rank + rot_dim and pool.dtype == proj.dtype
+    assert (q_out is None) == (q_weight is None)
+    assert q_out is None or (q_out.dtype == proj.dtype and q_out.shape == (tokens, q_rank)
+                             and q_weight.dtype == torch.float32 and q_weight.numel() == q_rank)
     assert inv_freq.dtype == torch.float32 and inv_freq.numel() * 2 == rot_dims
     writes = kv_off is not None and store
     assert not writes or (kv_weight.dtype == torch.float32 and kv_weight.numel() == kv_rank)
     _check(_fn("li_latent_prep")(_code(proj), proj.data_ptr(), proj.stride(0), q_off, q_rank, kv_off if writes else -1,
-                                 kv_rank, rot_dim, rot_dims, q_weight.data_ptr(), _ptr(kv_weight if writes else None),
+                                 kv_rank, rot_dim, rot_dims, _ptr(q_weight), _ptr(kv_weight if writes else None),
                                  float(eps), inv_freq.data_ptr(), positions.data_ptr(), seq_of_token.data_ptr(),
                                  block_table.data_ptr(), block_table.stride(0), pool.data_ptr(), page_size,
-                                 pages if writes else 0, q_out.data_ptr(), tokens, _stream()), "latent_prep")
+                                 pages if writes else 0, _ptr(q_out), tokens, float(cos_sin_scale), _stream()),
+           "latent_prep")
 
 
 def latent_attention(q_lat: torch.Tensor, q_raw: torch.Tensor, q_head_stride: int, q_rot_off: int, out: torch.Tensor,
                      pool: torch.Tensor, block_table: torch.Tensor, query_start_loc: torch.Tensor,
                      context_lens: torch.Tensor, inv_freq: torch.Tensor, sink: torch.Tensor | None, num_seqs: int,
                      max_q_len: int, heads: int, kv_rank: int, rot_dim: int, rot_dims: int, scale: float,
-                     plan=None) -> torch.Tensor:
+                     plan=None, window: int = 0, cos_sin_scale: float = 1.0) -> torch.Tensor:
     """Causal multi-query attention of every head over the shared cache entries [latent | rotated key part]:
     score = (q_lat . latent + rotate(q_rot) . key part) * scale, out = sum_j p_j latent_j, with exp(sink[h]) as one
     more term of the softmax's denominator (sink float32 [heads] or None).  q_lat, out: [heads, tokens, kv_rank];
     q_raw [tokens, columns]: the part of head h that turns lies at columns h * q_head_stride + q_rot_off (rot_dim
-    numbers, rotated here by the query's position).  pool [pages, 1, page_size, kv_rank + rot_dim]."""
-    _on_gpu(q_lat, q_raw, out, pool, block_table, query_start_loc, context_lens, inv_freq, sink)
+    numbers, rotated here by the query's position).  pool [pages, 1, page_size, kv_rank + rot_dim].  `window` > 0:
+    the query at position i sees the keys j with 0 <= i - j < window.  `cos_sin_scale` multiplies every cosine and
+    sine of the query's rotation."""
+    _on_gpu(q_lat, out, pool, block_table, query_start_loc, context_lens, inv_freq, sink)
+    _rows2d(q_raw, "q_raw")         # a column slice of a wider projection is fine
     _int32(block_table, "block_table"); _int32(query_start_loc, "query_start_loc"); _int32(context_lens, "context_lens")
     pages, one, page_size, entry = pool.shape
     tokens = q_raw.shape[0]
@@ -1350,7 +1396,7 @@ def latent_attention(q_lat: torch.Tensor, q_raw: torch.Tensor, q_head_stride: in
                 block_table.stride(0), query_start_loc.data_ptr(), context_lens.data_ptr(), _ptr(seq_index),
                 inv_freq.data_ptr(), _ptr(sink), count, q_len, heads, kv_rank, rot_dim, rot_dims, page_size, pages,
                 float(scale), splits, _ptr(partial_out), _ptr(partial_lse), tokens, int(two_blocks),
-                scratch_for(out.device).gemm_error.data_ptr(), _stream()),
+                scratch_for(out.device).gemm_error.data_ptr(), int(window), float(cos_sin_scale), _stream()),
                 "latent_attention_mma")
 
         if plan is None:
@@ -1360,7 +1406,8 @@ def latent_attention(q_lat: torch.Tensor, q_raw: torch.Tensor, q_head_stride: in
             run(plan.prefill_seqs, plan.num_prefill, max(plan.max_prefill_query_len, 2))
         if plan.num_decode:
             chunks = -(-heads // 16)
-            tiles = max(1, -(-plan.max_decode_context_len // 64))            # two tiles of 32 keys a split at least
+            reach = plan.max_decode_context_len if window <= 0 else min(plan.max_decode_context_len, window + 64)
+            tiles = max(1, -(-reach // 64))                                   # two tiles of 32 keys a split at least
             # Two blocks of eight warps per SM where the batch is wide (measured at 16 heads over 2,048 keys: 67
             # against 86 us at 64 sequences), one of sixteen where it is narrow (18.7 against 19.8 us at 8); as many
             # splits as still make one wave of either.
@@ -1372,7 +1419,8 @@ def latent_attention(q_lat: torch.Tensor, q_raw: torch.Tensor, q_head_stride: in
         _code(q_raw), q_lat.data_ptr(), q_lat.stride(0), q_lat.stride(1), q_raw.data_ptr(), q_raw.stride(0),
         q_head_stride, q_rot_off, out.data_ptr(), out.stride(0), out.stride(1), pool.data_ptr(), block_table.data_ptr(),
         block_table.stride(0), query_start_loc.data_ptr(), context_lens.data_ptr(), inv_freq.data_ptr(), _ptr(sink),
-        num_seqs, max_q_len, heads, kv_rank, rot_dim, rot_dims, page_size, pages, float(scale), _stream()),
+        num_seqs, max_q_len, heads, kv_rank, rot_dim, rot_dims, page_size, pages, float(scale), int(window),
+        float(cos_sin_scale), _stream()),
         "latent_attention")
     return out
 
@@ -1401,6 +1449,92 @@ def gate_heads(v: torch.Tensor, gate: torch.Tensor | None, out: torch.Tensor) ->
         assert gate.shape == out.shape and gate.dtype == v.dtype
     _check(_fn("li_gate_heads")(_code(v), v.data_ptr(), _ptr(gate), gate.stride(0) if gate is not None else 0,
                                 out.data_ptr(), tokens, heads, e, _stream()), "gate_heads")
+    return out
+
+
+# ------------------------------------------------------------- mixture of experts
+EXPERT_ACTIVATIONS = {"swiglu": 0, "capped_swiglu": 1}
+
+
+@dataclass
+class ExpertPlan:
+    """A step's (token, slot) pairs ordered by expert and cut into tiles of `tile_rows` rows of one expert each."""
+    order: torch.Tensor         # [pairs] int32: the pairs (token * top + slot), expert by expert
+    offsets: torch.Tensor       # [experts + 1] int32: where each expert's run starts in `order`
+    tile_expert: torch.Tensor   # [max_tiles] int32: the expert of each tile (-1: no such tile)
+    tile_row0: torch.Tensor     # [max_tiles] int32: its first row in `order`
+    tile_rows: int
+    max_tiles: int
+
+
+def moe_route(logits: torch.Tensor, top: int, groups: int, keep: int, renormalise: bool, ids: torch.Tensor,
+              weights: torch.Tensor) -> None:
+    """Per token of `logits` [tokens, experts] (float32): scores = softmax over all experts; with `groups` > 1 the
+    experts form that many equal groups of neighbours, a group's score is its largest, and only experts of the best
+    `keep` groups can be chosen; ids [tokens, top] int32 = the experts with the largest scores (ties: the lower
+    index), weights [tokens, top] float32 = their scores (`renormalise`: divided by their sum)."""
+    _on_gpu(logits, ids, weights)
+    _int32(ids, "ids")
+    tokens, experts = logits.shape
+    assert logits.dtype == torch.float32 == weights.dtype and logits.is_contiguous()
+    assert ids.shape == weights.shape == (tokens, top) and ids.is_contiguous() and weights.is_contiguous()
+    _check(_fn("li_moe_route")(logits.data_ptr(), tokens, experts, top, groups, keep, int(renormalise), ids.data_ptr(),
+                               weights.data_ptr(), _stream()), "moe_route")
+
+
+def moe_tile_rows(dtype: torch.dtype, hidden: int, ff: int) -> int:
+    """Rows of a tile of `moe_grouped`: 64 where both of an expert's products run on tensor cores, else 32."""
+    if not torch.cuda.is_available():
+        return 32
+    code = _DTYPE_CODE[dtype]
+    both = _fn("li_moe_tile_rows")(code, ff, hidden) == 64 and _fn("li_moe_tile_rows")(code, hidden, ff) == 64
+    return 64 if both else 32
+
+
+def moe_sort(ids: torch.Tensor, experts: int, tile_rows: int) -> ExpertPlan:
+    """The plan of a step whose pair p = token * top + slot goes to expert ids.flatten()[p]."""
+    _on_gpu(ids)
+    _int32(ids, "ids")
+    pairs = ids.numel()
+    max_tiles = -(-pairs // tile_rows) + experts
+    scratch = torch.empty(pairs + experts + 1 + 2 * max_tiles, dtype=torch.int32, device=ids.device)
+    order, offsets = scratch[:pairs], scratch[pairs:pairs + experts + 1]
+    tile_expert = scratch[pairs + experts + 1:pairs + experts + 1 + max_tiles]
+    tile_row0 = scratch[pairs + experts + 1 + max_tiles:]
+    _check(_fn("li_moe_sort")(ids.data_ptr(), pairs, experts, tile_rows, offsets.data_ptr(), order.data_ptr(),
+                              tile_expert.data_ptr(), tile_row0.data_ptr(), max_tiles, _stream()), "moe_sort")
+    return ExpertPlan(order, offsets, tile_expert, tile_row0, tile_rows, max_tiles)
+
+
+def moe_grouped(mode: str, a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, plan: ExpertPlan, top: int,
+                activation: str = "swiglu", limit: float = 0.0, alpha: float = 1.0,
+                pair_weights: torch.Tensor | None = None) -> torch.Tensor:
+    """The experts' products, grouped by expert.  mode "gate_up": out[p] = act(W_gate,e a[p // top], W_up,e a[p // top])
+    for pair p of expert e; a [tokens, hidden], weight [experts, 2 * ff, hidden] (an expert's gate rows, then its up
+    rows), out [pairs, ff]; `activation` of `EXPERT_ACTIVATIONS` ("capped_swiglu": g' = min(g, limit), u' = clamp(u,
+    -limit, limit), g' * sigmoid(alpha * g') * (u' + 1)).  mode "down": out[p] = (W_down,e a[p]) * pair_weights[p];
+    a [pairs, ff], weight [experts, hidden, ff], out [pairs, hidden]."""
+    _on_gpu(a, weight, out, pair_weights)
+    _rows2d(a, "a")
+    assert mode in ("gate_up", "down") and a.dtype == weight.dtype == out.dtype and out.is_contiguous()
+    experts, rows, K = weight.shape
+    N = rows // 2 if mode == "gate_up" else rows
+    assert weight.is_contiguous() and a.shape[1] == K and out.shape == (plan.order.numel(), N)
+    assert pair_weights is None or (pair_weights.dtype == torch.float32 and pair_weights.numel() == plan.order.numel())
+    _check(_fn("li_moe_grouped")(_code(a), 0 if mode == "gate_up" else 1, a.data_ptr(), a.stride(0), weight.data_ptr(),
+                                 out.data_ptr(), out.stride(0), plan.order.data_ptr(), plan.offsets.data_ptr(),
+                                 plan.tile_expert.data_ptr(), plan.tile_row0.data_ptr(), _ptr(pair_weights), top, N, K,
+                                 EXPERT_ACTIVATIONS[activation], float(limit), float(alpha), plan.max_tiles,
+                                 plan.tile_rows, _stream()), "moe_grouped")
+    return out
+
+
+def moe_combine(y: torch.Tensor, out: torch.Tensor, top: int) -> torch.Tensor:
+    """out[t] = sum over s < top of y[t * top + s], in slot order, summed in 32-bit."""
+    _on_gpu(y, out)
+    tokens, width = out.shape
+    assert y.shape == (tokens * top, width) and y.dtype == out.dtype and y.is_contiguous() and out.is_contiguous()
+    _check(_fn("li_moe_combine")(_code(y), y.data_ptr(), out.data_ptr(), tokens, top, width, _stream()), "moe_combine")
     return out
 
 

@@ -34,7 +34,11 @@ class Attention:
     `qk_norm` "projection": q and k are each divided by their root mean square over the
     whole projection (all heads at once; eps `qk_norm_eps`) and multiplied by the weights
     `q_norm.weight` / `k_norm.weight`, before the position encoding; "head": each head of q and of k is divided
-    by its own root mean square and multiplied by a weight of `head_dim` entries that the heads share.
+    by its own root mean square and multiplied by a weight of `head_dim` entries that the heads share
+    (`qk_norm_weight` False: by no weight; `qk_norm_after_rotation`: the norm comes behind the position encoding).
+    `sink`: a learned number per head (`sink`, 32-bit) whose exponential joins the denominator of that head's
+    softmax; it has no key and no value and is not scaled.  `output_gate`: the concatenated heads are multiplied
+    element by element by sigmoid(`gate_proj.weight` x) before the output projection.
     `head_gate`: head h of the attention's output is multiplied by sigmoid(g_h), g = `g_proj.weight` x, one number
     per head, before the output projection.  `value_mix`: "source" leaves this layer's values of the step's tokens
     in `ctx.extras[value_mix_key]` for later layers; "mixed" stores (1 - l) v + l v_source instead of v, l the
@@ -47,13 +51,21 @@ class Attention:
                  window: int | None = None, scale: float | None = None, cache_name: str = "kv",
                  v_head_dim: int | None = None, keep_first: int = 0, softcap: float = 0.0,
                  qk_norm: str | None = None, qk_norm_eps: float = 1e-6, head_gate: bool = False,
-                 value_mix: str | None = None, value_mix_key: str = "value_mix") -> None:
+                 value_mix: str | None = None, value_mix_key: str = "value_mix", qk_norm_weight: bool = True,
+                 qk_norm_after_rotation: bool = False, sink: bool = False, output_gate: bool = False) -> None:
         if heads % kv_heads:
             raise ValueError(f"heads={heads} is not a multiple of kv_heads={kv_heads}")
         if qk_norm not in (None, "projection", "head"):
             raise ValueError(f"qk_norm {qk_norm!r} is not supported; known: None, 'projection', 'head'")
         if value_mix not in (None, "source", "mixed"):
             raise ValueError(f"value_mix {value_mix!r} is not supported; known: None, 'source', 'mixed'")
+        if (not qk_norm_weight or qk_norm_after_rotation) and qk_norm != "head":
+            raise ValueError("a norm without a weight, or behind the rotation, is an option of qk_norm='head'")
+        if head_gate and output_gate:
+            raise ValueError("an attention has one gate: per head (head_gate) or per element (output_gate)")
+        self.qk_norm_weight, self.qk_norm_after_rotation = bool(qk_norm_weight), bool(qk_norm_after_rotation)
+        self.has_sink, self.output_gate = bool(sink), bool(output_gate)
+        self.sink: torch.Tensor | None = None
         self.head_gate, self.value_mix, self.value_mix_key = bool(head_gate), value_mix, value_mix_key
         self.blend: torch.Tensor | None = None
         self.hidden_size, self.heads, self.kv_heads, self.head_dim = hidden_size, heads, kv_heads, head_dim
@@ -83,13 +95,18 @@ class Attention:
             "o_proj.weight": TensorSpec((self.hidden_size, self.heads * self.v_head_dim)),
         }
         if self.qk_norm == "head":
-            specs.update({"q_norm.weight": TensorSpec((self.head_dim,), init="ones_normal"),
-                          "k_norm.weight": TensorSpec((self.head_dim,), init="ones_normal")})
+            if self.qk_norm_weight:
+                specs.update({"q_norm.weight": TensorSpec((self.head_dim,), init="ones_normal"),
+                              "k_norm.weight": TensorSpec((self.head_dim,), init="ones_normal")})
         elif self.qk_norm:
             specs.update({"q_norm.weight": TensorSpec((q,), init="ones_normal"),
                           "k_norm.weight": TensorSpec((kv,), init="ones_normal")})
         if self.head_gate:
             specs["g_proj.weight"] = TensorSpec((self.heads, self.hidden_size))
+        if self.output_gate:
+            specs["gate_proj.weight"] = TensorSpec((self.heads * self.v_head_dim, self.hidden_size))
+        if self.has_sink:
+            specs["sink"] = TensorSpec((self.heads,), kind="f32", init=_sink_init)
         if self.value_mix == "mixed":
             specs["value_mix"] = TensorSpec((), kind="f32", init=_blend_init)
         if self.bias:
@@ -104,21 +121,36 @@ class Attention:
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
         weights = [tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]]
         biases = [tensors[n] for n in ("q_proj.bias", "k_proj.bias", "v_proj.bias")] if self.bias else []
-        if self.head_gate:
+        order = self.position.pair_order() if hasattr(self.position, "pair_order") else None
+        if order is not None:
+            # The checkpoint pairs neighbouring dimensions: every head's rows of q and k (and what belongs to those
+            # dimensions) are brought into the order whose pairs are half a rotary width apart.
+            at = torch.tensor(order, device=weights[0].device)
+            per_head = lambda t: t.unflatten(0, (-1, self.head_dim))[:, at].flatten(0, 1)
+            weights[0], weights[1] = per_head(weights[0]), per_head(weights[1])
+            if self.bias:
+                biases[0], biases[1] = per_head(biases[0]), per_head(biases[1])
+        if self.head_gate or self.output_gate:
             # The gate's rows ride behind v, filled up to a multiple of 16 rows (what the products' tiles like).
-            gate = tensors["g_proj.weight"]
-            pad = -(sum(w.shape[0] for w in weights) + self.heads) % 16
+            gate = tensors["g_proj.weight" if self.head_gate else "gate_proj.weight"]
+            pad = -(sum(w.shape[0] for w in weights) + gate.shape[0]) % 16
             weights += [gate, gate.new_zeros((pad, self.hidden_size))]
             if self.bias:
-                biases.append(biases[0].new_zeros(self.heads + pad))
+                biases.append(biases[0].new_zeros(gate.shape[0] + pad))
         self.qkv_weight = torch.cat(weights).contiguous()
         if self.bias:
             self.qkv_bias = torch.cat(biases).contiguous()
         if self.value_mix == "mixed":
             self.blend = tensors["value_mix"].to(torch.float32).reshape(1).contiguous()
         self.o_weight = tensors["o_proj.weight"]
-        if self.qk_norm:
+        if self.qk_norm and self.qk_norm_weight:
             self.q_norm_weight, self.k_norm_weight = tensors["q_norm.weight"], tensors["k_norm.weight"]
+            if order is not None and self.qk_norm == "head":
+                self.q_norm_weight, self.k_norm_weight = self.q_norm_weight[at].contiguous(), self.k_norm_weight[at].contiguous()
+            elif order is not None:
+                self.q_norm_weight, self.k_norm_weight = per_head(self.q_norm_weight), per_head(self.k_norm_weight)
+        if self.has_sink:
+            self.sink = tensors["sink"].to(torch.float32).contiguous()
         self.o_bias = tensors.get("o_proj.bias") if self.out_bias else None
         self.position.bind({n[len("position."):]: t for n, t in tensors.items() if n.startswith("position.")})
 
@@ -137,7 +169,7 @@ class Attention:
         v_width = self.kv_heads * self.v_head_dim
         qkv = torch.empty((tokens, self.qkv_weight.shape[0]), dtype=x.dtype, device=x.device)
         ops.linear(x, self.qkv_weight, qkv, self.qkv_bias)
-        if self.qk_norm == "head" or self.head_gate or self.value_mix:
+        if self.qk_norm == "head" or self.head_gate or self.output_gate or self.value_mix:
             return self._forward_prepared(qkv, ctx, cache, residual)
         if self.qk_norm:
             ops.qk_projection_rmsnorm_(qkv[:, :q_width], self.q_norm_weight, qkv[:, q_width:q_width + kv_width],
@@ -146,6 +178,8 @@ class Attention:
         rotary = self.position.rotary()
         attended = torch.empty((tokens, self.heads * self.v_head_dim), dtype=x.dtype, device=x.device)
         masked = dict(keep_first=self.keep_first, softcap=self.softcap) if (self.keep_first or self.softcap) else {}
+        if self.sink is not None:
+            masked["sink"] = self.sink
         plain = not masked and self.v_head_dim == self.head_dim and (rotary is None or rotary.attention_scaling == 1.0)
         if plain and rotary is not None and ops.fused_decode_supports(x.dtype, self.heads, self.kv_heads, self.head_dim,
                                                                       rotary.rotary_dim, ctx.plan):
@@ -197,14 +231,19 @@ class Attention:
                 raise ValueError("a layer that mixes values runs behind the layer whose values it mixes in, "
                                  "with values of the same shape")
         per_head = self.qk_norm == "head"
+        options = {}
+        if per_head and (not self.qk_norm_weight or self.qk_norm_after_rotation):
+            options = dict(unit_norm=not self.qk_norm_weight, norm_after_rotation=self.qk_norm_after_rotation)
         ops.head_norm_rope_kv_write(qkv, ctx.positions, ctx.seq_of_token, table, kv.k_pool, kv.v_pool,
                                     rotary.inv_freq if rotary else None, self.heads, self.kv_heads, self.head_dim,
                                     rotary.rotary_dim if rotary else 0,
                                     self.q_norm_weight if per_head else None, self.k_norm_weight if per_head else None,
                                     self.qk_norm_eps, store=not cache.read_only, v_other=other,
-                                    blend=self.blend if other is not None else None)
+                                    blend=self.blend if other is not None else None, **options)
         attended = torch.empty((tokens, self.heads * self.v_head_dim), dtype=qkv.dtype, device=qkv.device)
         masked = dict(keep_first=self.keep_first, softcap=self.softcap) if (self.keep_first or self.softcap) else {}
+        if self.sink is not None:
+            masked["sink"] = self.sink
         ops.paged_attention(qkv, qkv.shape[1], attended, kv.k_pool, kv.v_pool, table, ctx.query_start_loc,
                             ctx.context_lens, ctx.num_seqs, ctx.max_query_len, self.heads, self.kv_heads,
                             self.head_dim, self.scale, self.window or 0, plan=ctx.plan,
@@ -212,7 +251,14 @@ class Attention:
         if self.head_gate:
             gate_at = q_width + kv_width + v_width
             ops.sigmoid_gate_heads_(attended, qkv[:, gate_at:gate_at + self.heads], self.heads)
+        elif self.output_gate:
+            gate_at = q_width + kv_width + v_width
+            ops.sigmoid_gate_(attended, qkv[:, gate_at:gate_at + self.heads * self.v_head_dim])
         return ops.linear(attended, self.o_weight, None, self.o_bias, residual=residual)
+
+
+def _sink_init(shape, generator):
+    return torch.randn(shape, generator=generator)
 
 
 def _blend_init(shape, generator):

@@ -34,7 +34,9 @@ class TokenEmbedding:
         # An id outside the table gives a zero row and raises the device's token flag, which
         # `ModelRunner.check_kernels` reports (the step function refuses such ids on the host before that).
         if self.scale != 1.0:
-            raise ValueError("a scaled embedding starts 32-bit streams (forward_streams); it has no output of the engine's dtype")
+            if self.weight.dtype == torch.float32:
+                return self.forward_streams(token_ids, 1)
+            raise ValueError("a scaled embedding starts a 32-bit stream (forward_streams); it has no output of the engine's dtype")
         return ops.embedding(token_ids, self.weight, out, ops.token_error_flag(token_ids.device))
 
     def forward_streams(self, token_ids: torch.Tensor, copies: int) -> torch.Tensor:
@@ -45,10 +47,13 @@ class TokenEmbedding:
 
 class LinearHead:
     """logits = x @ weight^T, no bias — liteinfer/models/llama.py:245,277.  A tied head
-    is bound to the embedding's tensor by the loader (llama.py:246-247)."""
+    is bound to the embedding's tensor by the loader (llama.py:246-247).  `softcap` c > 0: the logits become
+    c * tanh(logits / c)."""
 
-    def __init__(self, vocab_size: int, hidden_size: int, dtype: torch.dtype, device: torch.device) -> None:
+    def __init__(self, vocab_size: int, hidden_size: int, dtype: torch.dtype, device: torch.device,
+                 softcap: float | None = None) -> None:
         self.vocab_size, self.hidden_size = vocab_size, hidden_size
+        self.softcap = float(softcap) if softcap else 0.0
         self.weight: torch.Tensor | None = None
 
     def tensor_specs(self) -> dict[str, TensorSpec]:
@@ -60,7 +65,10 @@ class LinearHead:
     takes_pending_norm = True       # x may be an ops.PendingNorm: the product folds the final norm in
 
     def forward(self, x) -> torch.Tensor:
-        return ops.linear(x, self.weight, None)
+        logits = ops.linear(x, self.weight, None)
+        if self.softcap > 0:
+            ops.softcap_(logits, self.softcap)
+        return logits
 
 
 register_embedding("token_embedding", TokenEmbedding)

@@ -98,5 +98,76 @@ class DenseMLP:
         return ops.linear(hidden, self.down_weight, None)
 
 
+class RoutedExperts:
+    """A mixture of experts: every token runs `top` of `experts` small gated feed-forwards and adds up their
+    outputs, weighted by the router's scores.
+
+    Router: logits = `router.weight` x in 32-bit; scores = softmax over all experts.  With `groups` > 1 the experts
+    form that many equal groups of neighbours; a group's score is its largest score, and only experts of the best
+    `groups_keep` groups can be chosen.  The `top` largest scores among those are chosen; the weights are those
+    scores themselves (`renormalise`: divided by their sum).  Expert e: down_e(act(gate_e x, up_e x)), without
+    biases, `activation` of `ops.EXPERT_ACTIVATIONS` ("swiglu": silu(g) * u; "capped_swiglu": g' = min(g, limit),
+    u' = clamp(u, -limit, limit), g' * sigmoid(alpha * g') * (u' + 1)).  The step's (token, slot) pairs are ordered
+    by expert on the device, and both products run tile by tile over each expert's rows, so an expert's weights are
+    read once per tile of its tokens and nothing is read on the host.
+    """
+
+    def __init__(self, hidden_size: int, intermediate_size: int, experts: int, top: int, dtype: torch.dtype,
+                 device: torch.device, groups: int = 1, groups_keep: int = 1, activation: str = "swiglu",
+                 limit: float = 0.0, alpha: float = 1.0, renormalise: bool = False) -> None:
+        if activation not in ops.EXPERT_ACTIVATIONS:
+            raise ValueError(f"activation {activation!r} has no kernel; known: {sorted(ops.EXPERT_ACTIVATIONS)}")
+        if not 1 <= top <= experts or groups < 1 or experts % groups or not 1 <= groups_keep <= groups:
+            raise ValueError("a mixture of experts needs 1 <= top <= experts, groups that divide experts, and "
+                             "1 <= groups_keep <= groups")
+        if groups_keep * (experts // groups) < top:
+            raise ValueError("the kept groups hold fewer experts than `top`")
+        self.hidden_size, self.intermediate_size, self.experts, self.top = hidden_size, intermediate_size, experts, top
+        self.groups, self.groups_keep, self.activation = groups, groups_keep, activation
+        self.limit, self.alpha, self.renormalise = float(limit), float(alpha), bool(renormalise)
+        self.dtype, self.device = dtype, device
+        self.router = self.gate_up = self.down = None
+        self.tile_rows = 32
+
+    def tensor_specs(self) -> dict[str, TensorSpec]:
+        f, h = self.intermediate_size, self.hidden_size
+        specs = {"router.weight": TensorSpec((self.experts, h), kind="f32")}
+        for e in range(self.experts):
+            specs.update({f"experts.{e}.gate_proj.weight": TensorSpec((f, h)),
+                          f"experts.{e}.up_proj.weight": TensorSpec((f, h)),
+                          f"experts.{e}.down_proj.weight": TensorSpec((h, f))})
+        return specs
+
+    def bind(self, tensors: dict[str, torch.Tensor]) -> None:
+        self.router = tensors["router.weight"].to(torch.float32).contiguous()
+        # [experts, 2 * ff, hidden]: an expert's gate rows, then its up rows; [experts, hidden, ff].
+        self.gate_up = torch.stack([torch.cat([tensors[f"experts.{e}.gate_proj.weight"],
+                                               tensors[f"experts.{e}.up_proj.weight"]]) for e in range(self.experts)])
+        self.down = torch.stack([tensors[f"experts.{e}.down_proj.weight"] for e in range(self.experts)])
+        self.tile_rows = ops.moe_tile_rows(self.gate_up.dtype, self.hidden_size, self.intermediate_size)
+
+    def route(self, x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        """(chosen experts [tokens, top] int32, their weights [tokens, top] float32)."""
+        tokens = x.shape[0]
+        wide = x if x.dtype == torch.float32 else ops.convert(
+            x, torch.empty(x.shape, dtype=torch.float32, device=x.device))
+        logits = ops.linear(wide, self.router, None)
+        ids = torch.empty((tokens, self.top), dtype=torch.int32, device=x.device)
+        weights = torch.empty((tokens, self.top), dtype=torch.float32, device=x.device)
+        ops.moe_route(logits, self.top, self.groups, self.groups_keep, self.renormalise, ids, weights)
+        return ids, weights
+
+    def forward(self, x, ctx: StepContext):
+        tokens, pairs = x.shape[0], x.shape[0] * self.top
+        ids, weights = self.route(x)
+        plan = ops.moe_sort(ids, self.experts, self.tile_rows)
+        hidden = torch.empty((pairs, self.intermediate_size), dtype=x.dtype, device=x.device)
+        ops.moe_grouped("gate_up", x, self.gate_up, hidden, plan, self.top, self.activation, self.limit, self.alpha)
+        each = torch.empty((pairs, self.hidden_size), dtype=x.dtype, device=x.device)
+        ops.moe_grouped("down", hidden, self.down, each, plan, self.top, pair_weights=weights.view(-1))
+        return ops.moe_combine(each, torch.empty((tokens, self.hidden_size), dtype=x.dtype, device=x.device), self.top)
+
+
 register_feed_forward("gated_mlp", GatedMLP)
+register_feed_forward("routed_experts", RoutedExperts)
 register_feed_forward("dense_mlp", DenseMLP)

@@ -132,6 +132,10 @@ class Model:
         if self.spec.stream_copies is not None:
             # The residual is 32-bit streams: the embedding widens its rows itself and writes every copy.
             embedded, hidden = None, self.embedding.forward_streams(ctx.token_ids, self.spec.stream_copies)
+        elif self.wide_stream and getattr(self.embedding, "scale", 1.0) != 1.0:
+            # A scaled embedding starts the 32-bit stream itself: the row is widened before the multiply.
+            embedded = hidden = self.embedding.forward_streams(ctx.token_ids, 1)
+            return self._walk(hidden, embedded, ctx, caches)
         else:
             embedded = hidden = self.embedding.forward(ctx.token_ids)
         if self.wide_stream:
@@ -139,6 +143,9 @@ class Model:
             hidden = ops.convert(embedded, torch.empty(embedded.shape, dtype=torch.float32, device=embedded.device))
         elif self.reentry is not None:
             hidden = embedded.clone()       # the layers add into the stream in place; the embedding's output is read again
+        return self._walk(hidden, embedded, ctx, caches)
+
+    def _walk(self, hidden, embedded, ctx: StepContext, caches: list[LayerCache]):
         delta = None
         for stop, entry in enumerate(self.schedule):
             if entry.reenter:

@@ -95,22 +95,27 @@ def _around_zero(shape, generator):
     return 0.05 * torch.randn(shape, generator=generator)
 
 
-class UnitOffsetRMSNorm:
-    """y = x / sqrt(mean(x^2) + eps) * (1 + weight): a root-mean-square norm whose stored weight lies around zero.
+class AffineRMSNorm:
+    """y = x / sqrt(mean(x^2) + eps) * (offset + weight) * mult: a root-mean-square norm whose stored weight is
+    shifted by `offset` (0: the weight itself; 1: a stored weight that lies around zero) and whose result is
+    multiplied by the constant `mult` (a model that scales what a sublayer adds to its residual stream).
 
-    1 + weight is formed once, in 32-bit, when the tensors are bound.  Like `LayerNorm` it reads a stream that may
-    be 32-bit whatever the engine's dtype, writes the engine's dtype, and takes a pending `ops.NormedDelta`;
-    `normed_delta` makes one of a sublayer's output, for a block that normalises what a sublayer gives back."""
+    (offset + weight) * mult is formed once, in 32-bit, when the tensors are bound.  Like `LayerNorm` it reads a
+    stream that may be 32-bit whatever the engine's dtype, writes the engine's dtype, and takes a pending
+    `ops.NormedDelta`; `normed_delta` makes one of a sublayer's output, for a block that normalises what a sublayer
+    gives back."""
 
-    def __init__(self, size: int, eps: float, dtype: torch.dtype, device: torch.device) -> None:
+    def __init__(self, size: int, eps: float, dtype: torch.dtype, device: torch.device, offset: float = 0.0,
+                 mult: float = 1.0) -> None:
         self.size, self.eps, self.dtype, self.device = size, float(eps), dtype, device
-        self.weight: torch.Tensor | None = None         # 1 + the stored weight, float32
+        self.offset, self.mult = float(offset), float(mult)
+        self.weight: torch.Tensor | None = None         # (offset + the stored weight) * mult, float32
 
     def tensor_specs(self) -> dict[str, TensorSpec]:
-        return {"weight": TensorSpec((self.size,), kind="f32", init=_around_zero)}
+        return {"weight": TensorSpec((self.size,), kind="f32", init=_around_zero if self.offset else "ones_normal")}
 
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
-        self.weight = (1.0 + tensors["weight"].to(torch.float32)).contiguous()
+        self.weight = ((self.offset + tensors["weight"].to(torch.float32)) * self.mult).contiguous()
 
     def forward(self, x: torch.Tensor, delta: "torch.Tensor | ops.NormedDelta | None" = None,
                 rows: torch.Tensor | None = None, out: torch.Tensor | None = None):
@@ -126,6 +131,13 @@ class UnitOffsetRMSNorm:
     def normed_delta(self, value: torch.Tensor) -> "ops.NormedDelta":
         """What a sublayer's output becomes when this norm stands between it and the stream."""
         return ops.NormedDelta(value, self.weight, self.eps, centred=False)
+
+
+class UnitOffsetRMSNorm(AffineRMSNorm):
+    """y = x / sqrt(mean(x^2) + eps) * (1 + weight): `AffineRMSNorm` whose stored weight lies around zero."""
+
+    def __init__(self, size: int, eps: float, dtype: torch.dtype, device: torch.device) -> None:
+        super().__init__(size, eps, dtype, device, offset=1.0)
 
 
 class StreamRMSNorm:
@@ -163,3 +175,4 @@ register_norm("rmsnorm", RMSNorm)
 register_norm("stream_rmsnorm", StreamRMSNorm)
 register_norm("layernorm", LayerNorm)
 register_norm("rmsnorm_unit_offset", UnitOffsetRMSNorm)
+register_norm("rmsnorm_affine", AffineRMSNorm)

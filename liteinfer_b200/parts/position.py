@@ -80,13 +80,19 @@ def yarn_inverse_frequencies(dims: int, theta: float, factor: float, original: f
 class RotaryEmbedding:
     """Half-split rotary embedding: dimension j pairs with j + rotary_dim/2 (llama.py:89-102).  `rope_type`
     "yarn" takes `factor`, `original_max_position_embeddings`, `fast` and `slow` (`yarn_inverse_frequencies`).
-    `exact`: the plain frequencies computed in 64-bit and rounded once, instead of in 32-bit as the reference does."""
+    `exact`: the plain frequencies computed in 64-bit and rounded once, instead of in 32-bit as the reference does.
+    `pairs` "interleaved": the checkpoint pairs dimension 2i with 2i + 1.  The kernels rotate half-split pairs, so a
+    mixer brings the rows of its query and key projections into the order `pair_order()` when it binds them:
+    every score is a sum over the same products, in another order."""
 
     def __init__(self, head_dim: int, theta: float, dtype: torch.dtype, device: torch.device,
                  rotary_dim: int | None = None, rope_type: str = "default", factor: float = 1.0,
                  low_freq_factor: float = 1.0, high_freq_factor: float = 4.0,
                  original_max_position_embeddings: float = 0, fast: float | None = None,
-                 slow: float | None = None, exact: bool = False) -> None:
+                 slow: float | None = None, exact: bool = False, pairs: str = "half") -> None:
+        if pairs not in ("half", "interleaved"):
+            raise ValueError(f"pairs {pairs!r} is not supported; known: 'half', 'interleaved'")
+        self.head_dim, self.pairs = head_dim, pairs
         self.rotary_dim = head_dim if rotary_dim is None else rotary_dim
         scale = 1.0
         if exact:
@@ -114,6 +120,15 @@ class RotaryEmbedding:
     def rotary(self) -> RotaryTable | None:
         return self.table
 
+    def pair_order(self) -> list[int] | None:
+        """None where the checkpoint's pairs are half-split already; else, for a head (or rotated part) of
+        `head_dim` numbers, which stored dimension comes to stand at each place: the even ones of the first
+        `rotary_dim`, then the odd ones, then the rest as they are."""
+        if self.pairs == "half":
+            return None
+        r = self.rotary_dim
+        return list(range(0, r, 2)) + list(range(1, r, 2)) + list(range(r, self.head_dim))
+
     def apply(self, q: torch.Tensor, k: torch.Tensor, ctx) -> None:  # the fused path covers it
         raise NotImplementedError
 
@@ -131,6 +146,9 @@ class NoPositionEncoding:
         pass
 
     def rotary(self) -> RotaryTable | None:
+        return None
+
+    def pair_order(self) -> list[int] | None:
         return None
 
     def apply(self, q: torch.Tensor, k: torch.Tensor, ctx) -> None:

@@ -178,7 +178,7 @@ def _runs(seqs, positions):
 
 def paged_attention(q, q_row_stride, out, k_pool, v_pool, block_table, query_start_loc, context_lens, num_seqs,
                     max_q_len, heads, kv_heads, head_dim, scale, window=0, plan=None, decode_splits=None,
-                    keep_first=0, softcap=0.0):
+                    keep_first=0, softcap=0.0, sink=None):
     dtype = out.dtype
     v_dim = v_pool.shape[3]
     page_size = k_pool.shape[2]
@@ -214,8 +214,12 @@ def paged_attention(q, q_row_stride, out, k_pool, v_pool, block_table, query_sta
         hidden = hidden | (pages < 0)[None, :]
         scores = scores.masked_fill(hidden[None], float("-inf"))
         m = scores.amax(-1, keepdim=True)
+        if sink is not None:
+            m = torch.maximum(m, sink.float()[:, None, None])
         p = torch.exp(scores - m)
         denom = p.sum(-1, keepdim=True)
+        if sink is not None:
+            denom = denom + torch.exp(sink.float()[:, None, None] - m)
         o = torch.einsum("hqk,khd->qhd", _r(p, dtype), vals) / denom.permute(1, 0, 2)
         out[q0:q1] = o.reshape(n, heads * v_dim).to(dtype)
     return out
@@ -275,18 +279,23 @@ def gated_rmsnorm(x, gate, weight, eps, out, heads, gate_activation="silu", den=
 
 
 def head_norm_rope_kv_write(qkv, positions, seq_of_token, block_table, k_pool, v_pool, inv_freq, heads, kv_heads,
-                            head_dim, rotary_dim, q_norm, k_norm, norm_eps, store=True, v_other=None, blend=None):
-    """Per-head norms of q and k, the blend of v, then what `rope_kv_write` does, on a compact copy of the row."""
+                            head_dim, rotary_dim, q_norm, k_norm, norm_eps, store=True, v_other=None, blend=None,
+                            unit_norm=False, norm_after_rotation=False):
+    """Per-head norms of q and k, the blend of v, then what `rope_kv_write` does, on a compact copy of the row.
+    With the norm behind the rotation, q and k are rotated here and stored unrotated-as-they-are."""
     T, dtype = qkv.shape[0], qkv.dtype
     vd = v_pool.shape[-1]
     qw, kw, vw = heads * head_dim, kv_heads * head_dim, kv_heads * vd
     q = qkv[:, :qw].float().view(T, heads, head_dim)
     k = qkv[:, qw:qw + kw].float().view(T, kv_heads, head_dim)
     v = qkv[:, qw + kw:qw + kw + vw].float()
-    if q_norm is not None:
-        q = _norm(q, norm_eps, centre=False) * q_norm.float()
-    if k_norm is not None:
-        k = _norm(k, norm_eps, centre=False) * k_norm.float()
+    if norm_after_rotation and inv_freq is not None and rotary_dim > 0:
+        q, k = _turn(q, positions, inv_freq, rotary_dim), _turn(k, positions, inv_freq, rotary_dim)
+        inv_freq, rotary_dim = None, 0
+    if q_norm is not None or unit_norm:
+        q = _norm(q, norm_eps, centre=False) * (q_norm.float() if q_norm is not None else 1.0)
+    if k_norm is not None or unit_norm:
+        k = _norm(k, norm_eps, centre=False) * (k_norm.float() if k_norm is not None else 1.0)
     if v_other is not None:
         v = (1.0 - blend.float()) * v + blend.float() * v_other.float()
     # The norm's result is not rounded before the rotation (the kernel rounds once); float32 rows carry it over.
@@ -300,6 +309,16 @@ def head_norm_rope_kv_write(qkv, positions, seq_of_token, block_table, k_pool, v
     if dtype != torch.float32:
         k_pool.copy_(wide_k); v_pool.copy_(wide_v)
     qkv[:, :qw] = compact[:, :qw].to(dtype)
+
+
+def sigmoid_gate_(x, gate):
+    x.copy_((x.float() * torch.sigmoid(gate.float())).to(x.dtype))
+    return x
+
+
+def softcap_(x, cap):
+    x.copy_((cap * torch.tanh(x.float() / cap)).to(x.dtype))
+    return x
 
 
 def sigmoid_gate_heads_(x, gate, heads):
@@ -490,27 +509,30 @@ def batched_linear(x, weight, out):
     return out
 
 
-def _turn(x, positions, inv_freq, dims):
-    """Half-split rotation of the first `dims` numbers of the last axis of x [T, ..., n]."""
+def _turn(x, positions, inv_freq, dims, stretch=1.0):
+    """Half-split rotation of the first `dims` numbers of the last axis of x [T, ..., n]; `stretch` multiplies
+    every cosine and sine."""
     half = dims // 2
     angle = positions.float()[:, None] * inv_freq.float()[None, :]
     shape = [x.shape[0]] + [1] * (x.dim() - 2) + [half]
-    cos, sin = angle.cos().reshape(shape), angle.sin().reshape(shape)
+    cos, sin = angle.cos().reshape(shape) * stretch, angle.sin().reshape(shape) * stretch
     a, b = x[..., :half], x[..., half:dims]
     return torch.cat((a * cos - b * sin, b * cos + a * sin, x[..., dims:]), dim=-1)
 
 
 def latent_prep(proj, q_off, q_rank, kv_off, kv_rank, rot_dim, rot_dims, q_weight, kv_weight, eps, inv_freq, positions,
-                seq_of_token, block_table, pool, q_out, store=True):
+                seq_of_token, block_table, pool, q_out, store=True, cos_sin_scale=1.0):
     dtype = proj.dtype
     page_size = pool.shape[2]
-    q = proj[:, q_off:q_off + q_rank].float()
-    q_out.copy_((q / torch.sqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_weight).to(dtype))
+    if q_out is not None:
+        q = proj[:, q_off:q_off + q_rank].float()
+        q_out.copy_((q / torch.sqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_weight).to(dtype))
     if kv_off is None or not store:
         return
     latent = proj[:, kv_off:kv_off + kv_rank].float()
     latent = latent / torch.sqrt(latent.pow(2).mean(-1, keepdim=True) + eps) * kv_weight
-    shared = _turn(proj[:, kv_off + kv_rank:kv_off + kv_rank + rot_dim].float(), positions, inv_freq, rot_dims)
+    shared = _turn(proj[:, kv_off + kv_rank:kv_off + kv_rank + rot_dim].float(), positions, inv_freq, rot_dims,
+                   cos_sin_scale)
     entries = torch.cat([latent, shared], dim=-1).to(dtype)
     tables = block_table.tolist()
     for t, (seq, pos) in enumerate(zip(seq_of_token.tolist(), positions.tolist())):
@@ -522,7 +544,8 @@ def latent_prep(proj, q_off, q_rank, kv_off, kv_rank, rot_dim, rot_dims, q_weigh
 
 
 def latent_attention(q_lat, q_raw, q_head_stride, q_rot_off, out, pool, block_table, query_start_loc, context_lens,
-                     inv_freq, sink, num_seqs, max_q_len, heads, kv_rank, rot_dim, rot_dims, scale, plan=None):
+                     inv_freq, sink, num_seqs, max_q_len, heads, kv_rank, rot_dim, rot_dims, scale, plan=None, window=0,
+                     cos_sin_scale=1.0):
     dtype = out.dtype
     page_size = pool.shape[2]
     qsl, ctx = query_start_loc.tolist(), context_lens.tolist()
@@ -530,19 +553,22 @@ def latent_attention(q_lat, q_raw, q_head_stride, q_rot_off, out, pool, block_ta
                                      q_raw.device)
     flat = pool[:, 0].reshape(-1, kv_rank + rot_dim).float()
     tokens = q_raw.shape[0]
-    q_rot_all = q_raw[:, :heads * q_head_stride].float().view(tokens, heads, q_head_stride)[:, :, q_rot_off:q_rot_off + rot_dim]
+    q_rot_all = q_raw[:, :heads * q_head_stride].float().unflatten(1, (heads, q_head_stride))[:, :, q_rot_off:q_rot_off + rot_dim]
     for s in range(num_seqs):
         q0, q1 = qsl[s], qsl[s + 1]
         n, c = q1 - q0, ctx[s]
         if n == 0:
             continue
         qpos = torch.arange(c - n, c, device=q_raw.device)
-        q_rot = _r(_turn(q_rot_all[q0:q1], qpos, inv_freq, rot_dims), dtype)          # [n, H, r]
+        q_rot = _r(_turn(q_rot_all[q0:q1], qpos, inv_freq, rot_dims, cos_sin_scale), dtype)          # [n, H, r]
         q = torch.cat([q_lat[:, q0:q1].float(), q_rot.transpose(0, 1)], dim=-1)           # [H, n, c + r]
         slots = slots_of[s, :c]
         entries = flat[slots.clamp(min=0)]
         scores = torch.einsum("hqd,kd->hqk", q, entries) * scale
-        hidden = (torch.arange(c, device=q_raw.device)[None, :] > qpos[:, None]) | (slots < 0)[None, :]
+        kpos = torch.arange(c, device=q_raw.device)
+        hidden = (kpos[None, :] > qpos[:, None]) | (slots < 0)[None, :]
+        if window > 0:
+            hidden = hidden | (kpos[None, :] <= qpos[:, None] - window)
         scores = scores.masked_fill(hidden[None], float("-inf"))
         m = scores.amax(-1, keepdim=True)
         if sink is not None:
@@ -564,11 +590,67 @@ def gate_heads(v, gate, out):
     return out
 
 
+def moe_route(logits, top, groups, keep, renormalise, ids, weights):
+    scores = torch.softmax(logits.float(), dim=-1)
+    tokens, experts = scores.shape
+    allowed = torch.ones_like(scores, dtype=torch.bool)
+    if groups > 1:
+        per = experts // groups
+        best = scores.view(tokens, groups, per).amax(-1)
+        kept = torch.zeros(tokens, groups, dtype=torch.bool, device=scores.device)
+        kept.scatter_(1, best.topk(keep, dim=-1).indices, True)
+        allowed = kept.repeat_interleave(per, dim=1)
+    chosen = torch.where(allowed, scores, torch.full_like(scores, -1.0)).topk(top, dim=-1).indices
+    picked = scores.gather(1, chosen)
+    if renormalise:
+        picked = picked / picked.sum(-1, keepdim=True)
+    ids.copy_(chosen.to(torch.int32))
+    weights.copy_(picked)
+
+
+def moe_tile_rows(dtype, hidden, ff):
+    return 32
+
+
+class _Plan:
+    def __init__(self, ids, experts):
+        self.ids, self.experts = ids.reshape(-1).long(), experts
+        self.order = torch.argsort(self.ids, stable=True)
+
+
+def moe_sort(ids, experts, tile_rows):
+    return _Plan(ids, experts)
+
+
+def moe_grouped(mode, a, weight, out, plan, top, activation="swiglu", limit=0.0, alpha=1.0, pair_weights=None):
+    rows = weight.shape[1]
+    for pair, e in enumerate(plan.ids.tolist()):
+        w = weight[e].float()
+        if mode == "gate_up":
+            x = a[pair // top].float()
+            g, u = w[:rows // 2] @ x, w[rows // 2:] @ x
+            if activation == "capped_swiglu":
+                g, u = g.clamp(max=limit), u.clamp(min=-limit, max=limit)
+                y = g * torch.sigmoid(alpha * g) * (u + 1.0)
+            else:
+                y = g * torch.sigmoid(g) * u
+        else:
+            y = (w @ a[pair].float()) * (1.0 if pair_weights is None else pair_weights[pair])
+        out[pair] = y.to(out.dtype)
+    return out
+
+
+def moe_combine(y, out, top):
+    out.copy_(y.float().view(out.shape[0], top, -1).sum(1).to(out.dtype))
+    return out
+
+
 def fused_decode_supports(*args) -> bool:
     return False      # the stand-ins rotate and store in `rope_kv_write`, never inside the attention
 
 
-ALL = ("head_norm_rope_kv_write", "sigmoid_gate_heads_", "mlstm", "embedding_streams", "stream_rmsnorm", "activation", "batched_linear", "latent_prep", "latent_attention",
+ALL = ("moe_route", "moe_tile_rows", "moe_sort", "moe_grouped", "moe_combine", "sigmoid_gate_", "softcap_",
+       "head_norm_rope_kv_write", "sigmoid_gate_heads_", "mlstm", "embedding_streams", "stream_rmsnorm", "activation", "batched_linear", "latent_prep", "latent_attention",
        "gate_heads", "convert", "layernorm", "layernorm_add", "projection_rmsnorm_", "qk_projection_rmsnorm_", "gated_rmsnorm",
        "short_conv", "short_conv_step", "short_conv_update", "gated_delta_rule", "fused_decode_supports", "scatter_tokens", "embedding", "rmsnorm", "add_", "add_bias_", "act_mul", "act_mul_interleaved", "gated_linear_supported",
        "gated_linear", "gemm_error_flag", "error_flags", "token_error_flag", "linear", "gemm_simt", "rope_kv_write", "paged_attention", "argmax", "sample")
