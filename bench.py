@@ -17,6 +17,8 @@ decoder beside the Llama decoder at equal layer sizes, and the Kegizen kernels o
 `--compare gifudra` does the same for the Gifudra decoder (latent attention, residual streams).
 `--compare karupel` sets the Karupel decoder (mLSTM, delta-rule and gated attention layers) beside a Kegizen decoder of
 the same sizes, its closest relative, and its kernels beside their like.
+`--compare kutolix` sets the Kutolix decoder (windowed gated attention with a sink, windowed latent attention, dense
+and routed feed-forwards) beside a Gifudra decoder of the same sizes, and its kernels beside their like.
 """
 
 from __future__ import annotations
@@ -343,6 +345,27 @@ def _karupel_config(width: int, ff: int, layers: int, heads: int, kv_heads: int,
             "layers": [order[i % 4] for i in range(layers)]}
 
 
+def _kutolix_config(width: int, ff: int, layers: int, heads: int, kv_heads: int, head_dim: int, vocab: int) -> dict:
+    """Gated attention and latent attention in turn, both with a window of 1,024: the attention with the sizes of the
+    Llama layer at head size 128 (half of each head rotated), the latent attention with those of the Gifudra layer
+    (unrotated part 128, rotated part 64 with YaRN frequencies, values 128, a latent of 512); a dense feed-forward
+    behind the attention, 32 experts a quarter as wide behind the latent attention, of which each token runs four
+    (eight groups, four kept): as many feed-forward weights per token in either."""
+    h = heads * head_dim // 128
+    attention = {"type": "attention", "mlp": {"kind": "dense", "ff": ff},
+                 "mixer": {"heads": h, "kv_heads": max(1, h // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                           "mask": {"size": 1024}, "rot": {"dims": 64, "base": 250000.0}}}
+    latent = {"type": "latent_attention",
+              "mlp": {"kind": "moe", "expert": {"ff": ff // 4, "limit": 7.0},
+                      "router": {"experts": 32, "top": 4, "groups": {"count": 8, "keep": 4}}},
+              "mixer": {"heads": h, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "scale": 192 ** -0.5,
+                        "mask": {"size": 1024},
+                        "rot": {"dims": 64, "base": 10000.0,
+                                "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}}
+    return {"architecture": "Kutolix", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 0.5},
+            "residual_mult": 0.5, "logit_softcap": 15.0, "layers": [(attention, latent)[i % 2] for i in range(layers)]}
+
+
 def _timed(fn, repeats: int = 20, warmup: int = 5, inner: int = 1) -> float:
     """Median milliseconds of one `fn()` on the current stream, between CUDA events, after `warmup` calls; with
     `inner` > 1 that many calls stand between the events (a kernel shorter than the host's time to launch it)."""
@@ -659,6 +682,169 @@ def _karupel_kernels(peaks: dict) -> dict:
     return {k: round(v, 4) for k, v in out.items()}
 
 
+def _kutolix_kernels(peaks: dict) -> dict:
+    """Each kernel that the Kutolix design brought or changed, alone beside its like, as fractions of the measured
+    copy bandwidth (kernels that stream) or product throughput (attention and experts over prompts); inputs larger
+    than L2."""
+    import torch
+
+    from liteinfer_b200 import ops
+    from liteinfer_b200.parts.context import AttentionPlan
+
+    dev, bf = "cuda:0", torch.bfloat16
+    hbm, tflops = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops_burst"] * 1e12
+    out: dict = {}
+
+    def ints(v):
+        return torch.tensor(v, dtype=torch.int32, device=dev)
+
+    def in_graph(fn, inner: int = 10) -> float:
+        fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(inner):
+                fn()
+        return _timed(graph.replay, repeats=10, warmup=2) / inner
+
+    # -- gated attention (16 / 4 heads of 128, a window of 1,024, a sink) beside the same launch without a sink
+    H, kv_heads, hd, page, n, window = 16, 4, 128, 16, 2048, 1024
+    pages = n // page
+    sink = torch.zeros(H, device=dev)
+    k_pool = torch.randn(pages * 64, kv_heads, page, hd, device=dev).to(bf)
+    v_pool = torch.randn(pages * 64, kv_heads, page, hd, device=dev).to(bf)
+    table = torch.arange(pages, dtype=torch.int32, device=dev).view(1, pages)
+    q = torch.randn(n, H * hd, device=dev).to(bf)
+    o = torch.empty_like(q)
+    plan = AttentionPlan(num_prefill=1, prefill_seqs=ints([0]), max_prefill_query_len=n)
+    args = (q, q.shape[1], o, k_pool, v_pool, table, ints([0, n]), ints([n]), 1, n, H, kv_heads, hd, hd ** -0.5, window)
+    seen = n * (n + 1) // 2 - (n - window) * (n - window + 1) // 2          # (query, key) pairs inside the window
+    for name, extra in (("sink_attention", dict(sink=sink)), ("plain_attention", {})):
+        ms = _timed(lambda: ops.paged_attention(*args, plan=plan, **extra))
+        out[f"{name}_prompt_us"] = ms * 1e3
+        out[f"{name}_prompt_tflops_frac"] = 4 * H * hd * seen / (ms * 1e-3) / tflops
+    for B in (64, 8):
+        table = torch.arange(B * pages, dtype=torch.int32, device=dev).view(B, pages)
+        plan = AttentionPlan(num_decode=B, decode_seqs=ints(list(range(B))), decode_tokens=ints(list(range(B))),
+                             max_decode_context_len=n)
+        qsl, ctxl = ints(list(range(B + 1))), ints([n] * B)
+        q = torch.randn(B, H * hd, device=dev).to(bf)
+        o = torch.empty_like(q)
+        args = (q, q.shape[1], o, k_pool, v_pool, table, qsl, ctxl, B, 1, H, kv_heads, hd, hd ** -0.5, window)
+        for name, extra in (("sink_attention", dict(sink=sink)), ("plain_attention", {})):
+            ms = in_graph(lambda: ops.paged_attention(*args, plan=plan, **extra))
+            out[f"{name}_decode_b{B}_us"] = ms * 1e3
+            out[f"{name}_decode_b{B}_hbm_frac"] = B * window * kv_heads * hd * 2 * 2 / (ms * 1e-3) / hbm
+
+    # -- latent attention with a window of 1,024 (16 heads, latent 512 + 64 rotated) beside the same launch without
+    C, R, dm = 512, 64, 128
+    inv_freq = (10000.0 ** (-torch.arange(R // 2, dtype=torch.float64) * 2 / R)).float().to(dev)
+    pool = (torch.randn(pages * 64, 1, page, C + R, device=dev) * 0.3).to(bf)
+    table = torch.arange(pages, dtype=torch.int32, device=dev).view(1, pages)
+    q_lat, q_raw = (torch.randn(H, n, C, device=dev) * 0.3).to(bf), torch.randn(n, H * (dm + R), device=dev).to(bf)
+    o_lat = torch.empty_like(q_lat)
+    plan = AttentionPlan(num_prefill=1, prefill_seqs=ints([0]), max_prefill_query_len=n)
+    qsl, ctxl = ints([0, n]), ints([n])
+    for name, extra, pairs in (("windowed_latent", dict(window=window, cos_sin_scale=1.14), seen),
+                               ("causal_latent", {}, n * (n + 1) // 2)):
+        ms = _timed(lambda: ops.latent_attention(q_lat, q_raw, dm + R, dm, o_lat, pool, table, qsl, ctxl, inv_freq, None,
+                                                 1, n, H, C, R, R, 0.07, plan=plan, **extra))
+        out[f"{name}_prompt_us"] = ms * 1e3
+        out[f"{name}_prompt_tflops_frac"] = 2 * H * (2 * C + R) * pairs / (ms * 1e-3) / tflops
+    for B in (64, 8):
+        table = torch.arange(B * pages, dtype=torch.int32, device=dev).view(B, pages)
+        q_lat, q_raw = (torch.randn(H, B, C, device=dev) * 0.3).to(bf), torch.randn(B, H * (dm + R), device=dev).to(bf)
+        o_lat = torch.empty_like(q_lat)
+        plan = AttentionPlan(num_decode=B, decode_seqs=ints(list(range(B))), decode_tokens=ints(list(range(B))),
+                             max_decode_context_len=n)
+        qsl, ctxl = ints(list(range(B + 1))), ints([n] * B)
+        for name, extra, keys in (("windowed_latent", dict(window=window, cos_sin_scale=1.14), window), ("causal_latent", {}, n)):
+            ms = in_graph(lambda: ops.latent_attention(q_lat, q_raw, dm + R, dm, o_lat, pool, table, qsl, ctxl, inv_freq,
+                                                       None, B, 1, H, C, R, R, 0.07, plan=plan, **extra))
+            out[f"{name}_decode_b{B}_us"] = ms * 1e3
+            out[f"{name}_decode_b{B}_hbm_frac"] = B * keys * (C + R) * 2 / (ms * 1e-3) / hbm
+
+    # -- what stands in front of the gated attention (rotation of half a head, unit norm behind it, store) beside the
+    #    Karupel form (norm with a weight in front of the rotation); the element-wise gate beside the gate per head
+    T = 16384
+    heads, kvh = 32, 8
+    pages_t = T // page
+    row = (heads + 2 * kvh) * hd
+    qkv = torch.randn(T, row + heads * hd, device=dev).to(bf)
+    kp, vp = (torch.empty(pages_t, kvh, page, hd, dtype=bf, device=dev) for _ in range(2))
+    table = torch.arange(pages_t, dtype=torch.int32, device=dev).view(1, pages_t)
+    positions, seq_of = torch.arange(T, dtype=torch.int32, device=dev), torch.zeros(T, dtype=torch.int32, device=dev)
+    inv_half = (250000.0 ** (-torch.arange(0, hd // 2, 2, dtype=torch.float32) / (hd // 2))).to(dev)
+    norm_w = torch.ones(hd, dtype=bf, device=dev)
+    moved = T * hd * 2 * (2 * heads + 4 * kvh)
+    ms = _timed(lambda: ops.head_norm_rope_kv_write(qkv, positions, seq_of, table, kp, vp, inv_half, heads, kvh, hd, hd // 2,
+                                                    None, None, 1e-6, unit_norm=True, norm_after_rotation=True))
+    out["unit_norm_behind_rotation_store_hbm_frac"] = moved / (ms * 1e-3) / hbm
+    ms = _timed(lambda: ops.head_norm_rope_kv_write(qkv, positions, seq_of, table, kp, vp, inv_half, heads, kvh, hd, hd // 2,
+                                                    norm_w, norm_w, 1e-6))
+    out["karupel_head_norm_rope_store_hbm_frac"] = moved / (ms * 1e-3) / hbm
+    attended = torch.randn(T, heads * hd, device=dev).to(bf)
+    ms = _timed(lambda: ops.sigmoid_gate_(attended, qkv[:, row:]))
+    out["output_gate_hbm_frac"] = T * heads * hd * 2 * 3 / (ms * 1e-3) / hbm
+    ms = _timed(lambda: ops.sigmoid_gate_heads_(attended, qkv[:, row:row + heads], heads))
+    out["karupel_head_gate_hbm_frac"] = T * heads * hd * 2 * 2 / (ms * 1e-3) / hbm
+
+    # -- the routed feed-forward (width 2,048; 32 experts 2,048 wide; 4 per token) beside the dense one (8,192 wide)
+    W, F, E, top = 2048, 2048, 32, 4
+    gate_up = (torch.randn(E, 2 * F, W, device=dev) * 0.02).to(bf)
+    down = (torch.randn(E, W, F, device=dev) * 0.02).to(bf)
+    router = torch.randn(E, W, device=dev) * 0.02
+    dense_gate_up = (torch.randn(2 * 4 * F, W, device=dev) * 0.02).to(bf)
+    dense_down = (torch.randn(W, 4 * F, device=dev) * 0.02).to(bf)
+    tile = ops.moe_tile_rows(bf, W, F)
+    for tokens, key in ((2048, "prompt_2048"), (64, "decode_b64"), (8, "decode_b8")):
+        x = torch.randn(tokens, W, device=dev).to(bf)
+        ids, weights = torch.empty(tokens, top, dtype=torch.int32, device=dev), torch.empty(tokens, top, device=dev)
+        act, each = torch.empty(tokens * top, F, dtype=bf, device=dev), torch.empty(tokens * top, W, dtype=bf, device=dev)
+        y = torch.empty(tokens, W, dtype=bf, device=dev)
+        state = {}
+
+        def route():
+            logits = ops.linear(ops.convert(x, torch.empty(tokens, W, device=dev)), router, None)
+            ops.moe_route(logits, top, 8, 4, False, ids, weights)
+            state["plan"] = ops.moe_sort(ids, E, tile)
+
+        def experts():
+            ops.moe_grouped("gate_up", x, gate_up, act, state["plan"], top, "capped_swiglu", 7.0, 1.702)
+            ops.moe_grouped("down", act, down, each, state["plan"], top, pair_weights=weights.view(-1))
+            ops.moe_combine(each, y, top)
+
+        dense_hidden = torch.empty(tokens, 4 * F, dtype=bf, device=dev)
+        interleaved = ops.gated_linear_supported(x, dense_gate_up)
+
+        def dense():
+            if interleaved:
+                ops.gated_linear(x, dense_gate_up, dense_hidden, "silu")
+            else:
+                ops.act_mul(ops.linear(x, dense_gate_up, None), dense_hidden, "silu")
+            ops.linear(dense_hidden, dense_down, None)
+
+        route()
+        timer = _timed if tokens > 64 else in_graph
+        out[f"moe_route_sort_{key}_us"] = timer(route) * 1e3
+        ms_e, ms_d = timer(experts), timer(dense)
+        out[f"moe_experts_{key}_us"], out[f"dense_ff_{key}_us"] = ms_e * 1e3, ms_d * 1e3
+        flops = 2 * tokens * top * 3 * F * W
+        if tokens > 64:
+            out[f"moe_experts_{key}_tflops_frac"] = flops / (ms_e * 1e-3) / tflops
+            out[f"dense_ff_{key}_tflops_frac"] = flops / (ms_d * 1e-3) / tflops
+        else:
+            active = int(torch.unique(ids).numel())
+            out[f"moe_experts_{key}_active"] = active
+            out[f"moe_experts_{key}_hbm_frac"] = active * 3 * F * W * 2 / (ms_e * 1e-3) / hbm
+            out[f"dense_ff_{key}_hbm_frac"] = 3 * 4 * F * W * 2 / (ms_d * 1e-3) / hbm
+
+    # -- the soft cap on 64 rows of logits
+    logits = torch.randn(64, 32000, device=dev).to(bf)
+    out["softcap_b64_us"] = in_graph(lambda: ops.softcap_(logits, 15.0)) * 1e3
+    return {k: round(v, 4) for k, v in out.items()}
+
+
 def run_kegizen(args, which: str = "kegizen") -> dict:
     """Prefill (one prompt of 2,048 tokens) and decode (batch 8 and 64 near a context of 2,048) of a Kegizen (or
     Gifudra) model and of a Llama model with the same width, depth, head sizes and feed-forward, random weights,
@@ -679,7 +865,10 @@ def run_kegizen(args, which: str = "kegizen") -> dict:
     if which == "gifudra":      # heads of 128 in both sizes: the latent attention's heads are 128 + 64 wide
         sizes = {"w2048": dict(width=2048, ff=8192, layers=8, heads=16, kv_heads=4, head_dim=128),
                  "w4096": dict(width=4096, ff=14336, layers=4, heads=32, kv_heads=8, head_dim=128)}
-    design = {"gifudra": _gifudra_config, "karupel": _karupel_config}.get(which, _kegizen_config)
+    if which == "kutolix":
+        sizes = {"w2048": dict(width=2048, ff=8192, layers=8, heads=16, kv_heads=4, head_dim=128),
+                 "w4096": dict(width=4096, ff=14336, layers=4, heads=32, kv_heads=8, head_dim=128)}
+    design = {"gifudra": _gifudra_config, "karupel": _karupel_config, "kutolix": _kutolix_config}.get(which, _kegizen_config)
     result: dict = {"impl": "ours", "compare": which, "dtype": "bf16", "data": "synthetic ids, random weights",
                     "peaks": peaks, "models": {}}
     for name, size in sizes.items():
@@ -689,6 +878,8 @@ def run_kegizen(args, which: str = "kegizen") -> dict:
         beside = ("llama", llama)
         if which == "karupel":      # its closest relative: delta-rule layers and plain causal attention, the same sizes
             beside = ("kegizen", _kegizen_config(vocab=vocab, plain_attention=True, **size))
+        if which == "kutolix":      # its closest relative: latent attention with a sink and a gate, dense feed-forwards
+            beside = ("gifudra", _gifudra_config(vocab=vocab, **size))
         for arch, cfg in ((which, design(vocab=vocab, **size)), beside):
             with tempfile.TemporaryDirectory() as tmp:
                 model_dir = write_random_model(cfg, Path(tmp) / arch, seed=0)
@@ -716,7 +907,7 @@ def run_kegizen(args, which: str = "kegizen") -> dict:
                 runner.check_kernels()
                 llm.close()
                 result["models"][f"{name}_{arch}"] = numbers
-    kernels = {"gifudra": _gifudra_kernels, "karupel": _karupel_kernels}.get(which, _kegizen_kernels)
+    kernels = {"gifudra": _gifudra_kernels, "karupel": _karupel_kernels, "kutolix": _kutolix_kernels}.get(which, _kegizen_kernels)
     result["kernels"] = kernels(peaks)
     return result
 
@@ -858,10 +1049,10 @@ def main() -> int:
     parser.add_argument("--workload", default="none", choices=["none", "3b", "8b", "all"],
                         help="run the reference's larger configurations instead (64 requests under continuous batching "
                              "at the 3B sizes; decode at a context of 8,192 at the 8B sizes) and print their line")
-    parser.add_argument("--compare", default="none", choices=["none", "kegizen", "gifudra", "karupel"],
-                        help="instead of the default run: the Kegizen (or Gifudra) decoder beside the Llama decoder, or "
-                             "the Karupel decoder beside the Kegizen decoder, at equal layer sizes (prefill, decode, and "
-                             "the design's kernels one by one)")
+    parser.add_argument("--compare", default="none", choices=["none", "kegizen", "gifudra", "karupel", "kutolix"],
+                        help="instead of the default run: the Kegizen (or Gifudra) decoder beside the Llama decoder, "
+                             "the Karupel decoder beside the Kegizen decoder, or the Kutolix decoder beside the Gifudra "
+                             "decoder, at equal layer sizes (prefill, decode, and the design's kernels one by one)")
     parser.add_argument("--no-workloads", action="store_true",
                         help="leave the 3B and 8B configurations out of the default run (they add about 80 s)")
     args = parser.parse_args()

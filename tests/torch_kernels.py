@@ -202,6 +202,8 @@ def paged_attention(q, q_row_stride, out, k_pool, v_pool, block_table, query_sta
         pages = torch.where(slots >= 0, slots // page_size, slots)
         keys = k_flat[slots.clamp(min=0)].float()
         vals = v_flat[slots.clamp(min=0)].float()
+        keys = torch.where((slots >= 0)[:, None, None], keys, torch.zeros_like(keys))      # a page given back holds nothing
+        vals = torch.where((slots >= 0)[:, None, None], vals, torch.zeros_like(vals))
         keys = keys.repeat_interleave(groups, dim=1)
         vals = vals.repeat_interleave(groups, dim=1)
         scores = torch.einsum("qhd,khd->hqk", qmat[q0:q1], keys) * scale
@@ -564,6 +566,7 @@ def latent_attention(q_lat, q_raw, q_head_stride, q_rot_off, out, pool, block_ta
         q = torch.cat([q_lat[:, q0:q1].float(), q_rot.transpose(0, 1)], dim=-1)           # [H, n, c + r]
         slots = slots_of[s, :c]
         entries = flat[slots.clamp(min=0)]
+        entries = torch.where((slots >= 0)[:, None], entries, torch.zeros_like(entries))    # a page given back holds nothing
         scores = torch.einsum("hqd,kd->hqk", q, entries) * scale
         kpos = torch.arange(c, device=q_raw.device)
         hidden = (kpos[None, :] > qpos[:, None]) | (slots < 0)[None, :]
