@@ -796,23 +796,18 @@ def _kutolix_kernels(peaks: dict) -> dict:
     router = torch.randn(E, W, device=dev) * 0.02
     dense_gate_up = (torch.randn(2 * 4 * F, W, device=dev) * 0.02).to(bf)
     dense_down = (torch.randn(W, 4 * F, device=dev) * 0.02).to(bf)
-    tile = ops.moe_tile_rows(bf, W, F)
+    from liteinfer_b200.ops import kernels as op_kernels
+
     for tokens, key in ((2048, "prompt_2048"), (64, "decode_b64"), (8, "decode_b8")):
         x = torch.randn(tokens, W, device=dev).to(bf)
         ids, weights = torch.empty(tokens, top, dtype=torch.int32, device=dev), torch.empty(tokens, top, device=dev)
-        act, each = torch.empty(tokens * top, F, dtype=bf, device=dev), torch.empty(tokens * top, W, dtype=bf, device=dev)
         y = torch.empty(tokens, W, dtype=bf, device=dev)
-        state = {}
 
         def route():
-            logits = ops.linear(ops.convert(x, torch.empty(tokens, W, device=dev)), router, None)
-            ops.moe_route(logits, top, 8, 4, False, ids, weights)
-            state["plan"] = ops.moe_sort(ids, E, tile)
+            ops.moe_router(x, router, top, 8, 4, False, ids, weights)
 
         def experts():
-            ops.moe_grouped("gate_up", x, gate_up, act, state["plan"], top, "capped_swiglu", 7.0, 1.702)
-            ops.moe_grouped("down", act, down, each, state["plan"], top, pair_weights=weights.view(-1))
-            ops.moe_combine(each, y, top)
+            ops.moe_experts(x, gate_up, down, ids, weights, "capped_swiglu", 7.0, 1.702, True, y)
 
         dense_hidden = torch.empty(tokens, 4 * F, dtype=bf, device=dev)
         interleaved = ops.gated_linear_supported(x, dense_gate_up)
@@ -826,17 +821,25 @@ def _kutolix_kernels(peaks: dict) -> dict:
 
         route()
         timer = _timed if tokens > 64 else in_graph
-        out[f"moe_route_sort_{key}_us"] = timer(route) * 1e3
-        ms_e, ms_d = timer(experts), timer(dense)
-        out[f"moe_experts_{key}_us"], out[f"dense_ff_{key}_us"] = ms_e * 1e3, ms_d * 1e3
+        out[f"moe_router_{key}_us"] = timer(route) * 1e3
+        ms_d = timer(dense)
+        out[f"dense_ff_{key}_us"] = ms_d * 1e3
         flops = 2 * tokens * top * 3 * F * W
+        active = int(torch.unique(ids).numel())
+        for form, least in (("tcgen05", 1), ("mma", 1 << 30)):      # both forms of the experts' products at every width
+            kept = op_kernels.MOE_TCGEN05_MIN_PAIRS
+            op_kernels.MOE_TCGEN05_MIN_PAIRS = least
+            ms_e = timer(experts)
+            op_kernels.MOE_TCGEN05_MIN_PAIRS = kept
+            out[f"moe_experts_{form}_{key}_us"] = ms_e * 1e3
+            if tokens > 64:
+                out[f"moe_experts_{form}_{key}_tflops_frac"] = flops / (ms_e * 1e-3) / tflops
+            else:
+                out[f"moe_experts_{form}_{key}_hbm_frac"] = active * 3 * F * W * 2 / (ms_e * 1e-3) / hbm
         if tokens > 64:
-            out[f"moe_experts_{key}_tflops_frac"] = flops / (ms_e * 1e-3) / tflops
             out[f"dense_ff_{key}_tflops_frac"] = flops / (ms_d * 1e-3) / tflops
         else:
-            active = int(torch.unique(ids).numel())
             out[f"moe_experts_{key}_active"] = active
-            out[f"moe_experts_{key}_hbm_frac"] = active * 3 * F * W * 2 / (ms_e * 1e-3) / hbm
             out[f"dense_ff_{key}_hbm_frac"] = 3 * 4 * F * W * 2 / (ms_d * 1e-3) / hbm
 
     # -- the soft cap on 64 rows of logits

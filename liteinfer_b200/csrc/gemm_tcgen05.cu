@@ -31,7 +31,12 @@ constexpr int kTileK = 64;                 // 64 bf16 = 128 bytes = one swizzle 
 constexpr int kUmmaK = 16;
 constexpr int kGemmThreads = 192;          // loader, issuer, four epilogue warps
 constexpr int kPairThreads = 320;          // the kernel for pairs of CTAs: loader, issuer, eight epilogue warps
-__device__ __forceinline__ float gated_value(float gate, float up, int act) {
+__device__ __forceinline__ float gated_value(float gate, float up, int act, float limit = 0.f, float alpha = 1.f) {
+  if (act == 4) {     // an expert's capped form, all of it in 32-bit: min(g, L) * sigmoid(alpha * min(g, L)) * (clamp(u, -L, L) + 1)
+    gate = fminf(gate, limit);
+    up = fminf(fmaxf(up, -limit), limit);
+    return gate * (1.0f / (1.0f + expf(-alpha * gate))) * (up + 1.0f);
+  }
   gate = __bfloat162float(__float2bfloat16_rn(gate));
   up = __bfloat162float(__float2bfloat16_rn(up));
   float a;
@@ -61,6 +66,18 @@ struct GemmParams {
   int M, N, K;
   int gated_act;
   int* error_flag;
+  // A product grouped by expert (tile_expert != null; the single-CTA kernel only): x holds the rows of all experts,
+  // expert by expert (rows [offsets[e], offsets[e + 1]) are expert e's), w the experts' matrices one below the other
+  // (N rows each), and row tile t of the launch is 128 rows of expert tile_expert[t] (-1: no such tile) from row
+  // tile_row0[t] on.  Rows of a tile behind its expert's last are computed and not stored.
+  const int* tile_expert;
+  const int* tile_row0;
+  const int* offsets;
+  int row_tiles;
+  // out[m] is multiplied by row_scale[row_of[m]] where row_scale is given (an expert's output times its weight).
+  const int* row_of;
+  const float* row_scale;
+  float limit, alpha;           // of gated_act 4
 };
 
 // 32 consecutive columns of one output row, from the accumulator's registers to global memory: rounded to
@@ -69,6 +86,7 @@ struct GemmParams {
 __device__ __forceinline__ void store_chunk(const GemmParams& p, const unsigned (&r)[32], int m, int n0) {
   if (p.gated_act < 0) {
     bf16* dst = p.out + (size_t)m * p.N + n0;
+    const float scale = p.row_scale != nullptr ? p.row_scale[p.row_of[m]] : 1.0f;
     if (n0 + 32 <= p.N && (p.N % 8) == 0) {
 #pragma unroll
       for (int v = 0; v < 4; ++v) {
@@ -76,7 +94,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, const unsigned 
         unsigned* w = reinterpret_cast<unsigned*>(&pack);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          float lo = __uint_as_float(r[v * 8 + 2 * j]), hi = __uint_as_float(r[v * 8 + 2 * j + 1]);
+          float lo = __uint_as_float(r[v * 8 + 2 * j]) * scale, hi = __uint_as_float(r[v * 8 + 2 * j + 1]) * scale;
           if (p.bias) {
             lo += __bfloat162float(p.bias[n0 + v * 8 + 2 * j]);
             hi += __bfloat162float(p.bias[n0 + v * 8 + 2 * j + 1]);
@@ -90,7 +108,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, const unsigned 
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
         if (n0 + j < p.N) {
-          float v = __uint_as_float(r[j]);
+          float v = __uint_as_float(r[j]) * scale;
           if (p.bias) v += __bfloat162float(p.bias[n0 + j]);
           dst[j] = __float2bfloat16_rn(v);
         }
@@ -116,7 +134,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, const unsigned 
             gate += __bfloat162float(p.bias[n0 + col]);
             up += __bfloat162float(p.bias[n0 + col + 8]);
           }
-          v[e] = gated_value(gate, up, p.gated_act);
+          v[e] = gated_value(gate, up, p.gated_act, p.limit, p.alpha);
         }
         __nv_bfloat162 h = __floats2bfloat162_rn(v[0], v[1]);
         w[j] = *reinterpret_cast<unsigned*>(&h);
@@ -143,7 +161,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   __shared__ unsigned tmem_base_shared;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tiles_m = (p.M + kTileM - 1) / kTileM, tiles_n = (p.N + BN - 1) / BN;
+  const bool grouped = p.tile_expert != nullptr;
+  const int tiles_m = grouped ? p.row_tiles : (p.M + kTileM - 1) / kTileM, tiles_n = (p.N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
   const int k_blocks = (p.K + kTileK - 1) / kTileK;
 
@@ -183,12 +202,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
         int tm, tn;
         tile_coords(tile, tiles_m, tiles_n, tm, tn);
+        // A grouped product: the tile's rows start where its expert's run says, its weights where the expert's lie.
+        // All three roles skip a tile that the table does not have, each by its own look.
+        const int expert = grouped ? p.tile_expert[tm] : 0;
+        if (expert < 0) continue;
+        const int row0 = grouped ? p.tile_row0[tm] : tm * kTileM;
+        const int w_row0 = expert * p.N + tn * BN;
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1, p.error_flag, 1)) { ok = false; break; }
           mbar_expect_tx(full_bar(stage), kStageBytes);
           const unsigned a = base + stage * kStageBytes;
-          tma_load_2d(a, &map_x, full_bar(stage), kb * kTileK, tm * kTileM);
-          tma_load_2d(a + kBytesA, &map_w, full_bar(stage), kb * kTileK, tn * BN);
+          tma_load_2d(a, &map_x, full_bar(stage), kb * kTileK, row0);
+          tma_load_2d(a + kBytesA, &map_w, full_bar(stage), kb * kTileK, w_row0);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -203,9 +228,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       unsigned phase = 0;
       int local = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++local) {
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        if (grouped) {
+          int tm, tn;
+          tile_coords(tile, tiles_m, tiles_n, tm, tn);
+          if (p.tile_expert[tm] < 0) continue;
+        }
         const int buf = local & 1;
         const unsigned use = (unsigned)(local >> 1);
+        ++local;
         if (!mbar_wait(acc_empty_bar(buf), (use & 1) ^ 1, p.error_flag, 2)) { ok = false; break; }
         tcgen05_fence_after();
         const unsigned acc = tmem_base + (unsigned)(buf * BN);
@@ -227,14 +258,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     const int quarter = warp & 3;                 // the TMEM lanes this warp may read: 32 * (warp % 4) ...
     int local = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++local) {
+    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
       int tm, tn;
       tile_coords(tile, tiles_m, tiles_n, tm, tn);
+      const int expert = grouped ? p.tile_expert[tm] : 0;
+      if (expert < 0) continue;
+      const int m_end = grouped ? p.offsets[expert + 1] : p.M;
       const int buf = local & 1;
       const unsigned use = (unsigned)(local >> 1);
+      ++local;
       if (!mbar_wait(acc_full_bar(buf), use & 1, p.error_flag, 4)) { ok = false; break; }
       tcgen05_fence_after();
-      const int m = tm * kTileM + quarter * 32 + lane;
+      const int m = (grouped ? p.tile_row0[tm] : tm * kTileM) + quarter * 32 + lane;
       const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(buf * BN);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -243,7 +278,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         tmem_load32(taddr + c * 32, r);
         tmem_load_wait();
         const int n0 = tn * BN + c * 32;
-        if (m >= p.M || n0 >= p.N) continue;
+        if (m >= m_end || n0 >= p.N) continue;
         store_chunk(p, r, m, n0);
       }
       tcgen05_fence_before();
@@ -444,7 +479,7 @@ static int launch_gemm(const CUtensorMap& mx, const CUtensorMap& mw, const GemmP
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  const int tiles = ((p.M + kTileM - 1) / kTileM) * ((p.N + BN - 1) / BN);
+  const int tiles = (p.tile_expert != nullptr ? p.row_tiles : (p.M + kTileM - 1) / kTileM) * ((p.N + BN - 1) / BN);
   const int grid = tiles < sms ? tiles : sms;
   gemm_tcgen05_kernel<BN, STAGES><<<grid, kGemmThreads, smem, s>>>(mx, mw, p);
   return (int)cudaGetLastError();
@@ -521,5 +556,35 @@ LI_EXPORT int li_gemm_tcgen05(const void* x, const void* w, const void* bias, vo
   CUtensorMap mx, mw;
   if (!make_map(&mx, x, M, K, kTileM) || !make_map(&mw, w, N, K, wide ? 256 : 128)) return LI_ERR_UNSUPPORTED;
   GemmParams p{(bf16*)out, (const bf16*)bias, M, N, K, gated_act, error_flag};
+  return wide ? launch_gemm<256, 4>(mx, mw, p, sms, stream) : launch_gemm<128, 6>(mx, mw, p, sms, stream);
+}
+
+// The product grouped by expert: x [rows, K] holds every expert's rows one run after the other (offsets
+// [experts + 1]); w [experts * N, K] the experts' matrices one below the other; out [rows, N] (gated_act >= 0:
+// [rows, N / 2], the rows of each expert's w interleaved in eights, eight gate rows and then their eight up rows;
+// gated_act 4 is the experts' capped form with `limit` and `alpha`).  Row tile t (of `row_tiles`) is 128 rows of expert
+// tile_expert[t] from row tile_row0[t] on; -1: no such tile.  row_scale (with row_of, both optional): out[m] is
+// multiplied by row_scale[row_of[m]].  bfloat16; K a multiple of 8.
+LI_EXPORT int li_gemm_tcgen05_grouped(const void* x, const void* w, void* out, int rows, int N, int K, int experts,
+                                      int gated_act, float limit, float alpha, const int* tile_expert,
+                                      const int* tile_row0, const int* offsets, int row_tiles, const int* row_of,
+                                      const float* row_scale, int* error_flag, cudaStream_t stream) {
+  if (rows == 0 || N == 0 || row_tiles == 0) return 0;
+  if (K < 8 || (K % 8) || gated_act > 4 || (gated_act >= 0 && (N % 16)) || experts < 1) return LI_ERR_UNSUPPORTED;
+  if ((long)experts * N > 0x7fffffffL || !tile_expert || !tile_row0 || !offsets) return LI_ERR_UNSUPPORTED;
+  if ((row_scale != nullptr) != (row_of != nullptr)) return LI_ERR_UNSUPPORTED;
+  if (!aligned16(x) || !aligned16(w) || !aligned16(out)) return LI_ERR_ALIGNMENT;
+  static int sms = 0;
+  if (!sms) {
+    int device = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    if (sms <= 0) sms = 148;
+  }
+  const bool wide = N >= 256;
+  CUtensorMap mx, mw;
+  if (!make_map(&mx, x, rows, K, kTileM) || !make_map(&mw, w, experts * N, K, wide ? 256 : 128)) return LI_ERR_UNSUPPORTED;
+  GemmParams p{(bf16*)out, nullptr, rows, N, K, gated_act, error_flag, tile_expert, tile_row0, offsets, row_tiles,
+               row_of, row_scale, limit, alpha};
   return wide ? launch_gemm<256, 4>(mx, mw, p, sms, stream) : launch_gemm<128, 6>(mx, mw, p, sms, stream);
 }

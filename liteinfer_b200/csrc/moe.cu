@@ -12,6 +12,9 @@
 //                    (x = the pair's activated row; out [pairs, hidden]).  float32 and odd sizes run FFMA tiles whose
 //                    sums over k have a fixed order; bfloat16 runs mma.sync m16n8k16 tiles fed by cp.async.
 //   li_moe_combine   out[token] = sum over its slots of the pairs' rows, in slot order, in 32-bit.
+//   li_moe_router    the router's 32-bit product and li_moe_route in one launch.
+//   li_moe_gather    the pairs' token rows in the order of the experts' runs: the first operand of the grouped product
+//                    on the fifth-generation tensor cores (gemm_tcgen05.cu), which wants an expert's rows side by side.
 //
 // Activations of an expert (32-bit): 0: silu(g) * u.  1: g' = min(g, limit), u' = clamp(u, -limit, limit),
 // g' * sigmoid(alpha * g') * (u' + 1).
@@ -31,9 +34,10 @@ __device__ __forceinline__ float expert_activation(float g, float u, int act, fl
 }
 
 // ------------------------------------------------------------------------------------------ route
-// The index of the largest of v[0..n) that is >= 0 (ties: the lowest index); every lane gets it.
+// The index of the largest of v[0..n) (ties: the lowest index); every lane gets it.  Entries are scores >= 0 or marks
+// of -1 and -2; whatever they hold, the result is an index below n (a row of padding may bring anything).
 __device__ __forceinline__ int warp_argmax(const float* v, int n, int lane) {
-  float best = -1.0f;
+  float best = -3.0f;
   int at = 0x7fffffff;
   for (int i = lane; i < n; i += 32)
     if (v[i] > best) { best = v[i]; at = i; }
@@ -43,22 +47,15 @@ __device__ __forceinline__ int warp_argmax(const float* v, int n, int lane) {
     const int oa = __shfl_xor_sync(0xffffffffu, at, o);
     if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
   }
-  return at;
+  return min(at, n - 1);
 }
 
 constexpr int kRouteWarps = 4;
 
-__global__ void __launch_bounds__(kRouteWarps * 32)
-moe_route_kernel(const float* __restrict__ logits, int tokens, int experts, int top, int groups, int keep,
-                 int renormalise, int* __restrict__ ids, float* __restrict__ weights) {
-  extern __shared__ float route_smem[];       // per warp: scores[experts], group scores[groups]
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * kRouteWarps + warp;
-  grid_dependency_wait();
-  if (t >= tokens) return;
-  float* sc = route_smem + warp * (experts + groups);
-  float* gb = sc + experts;
-  const float* z = logits + (size_t)t * experts;
+// One warp routes one token: z [experts] its logits; sc [experts] and gb [groups] scratch in shared memory (sc may be z).
+__device__ __forceinline__ void route_token(const float* z, float* sc, float* gb, int lane, int t, int experts, int top,
+                                            int groups, int keep, int renormalise, int* __restrict__ ids,
+                                            float* __restrict__ weights) {
   float mx = -INFINITY;
   for (int e = lane; e < experts; e += 32) mx = fmaxf(mx, z[e]);
   mx = warp_max(mx);
@@ -69,7 +66,10 @@ moe_route_kernel(const float* __restrict__ logits, int tokens, int experts, int 
     sum += v;
   }
   const float inv = 1.0f / warp_sum(sum);
-  for (int e = lane; e < experts; e += 32) sc[e] *= inv;
+  for (int e = lane; e < experts; e += 32) {
+    const float score = sc[e] * inv;
+    sc[e] = score >= 0.f ? score : 0.f;       // a row of padding may hold anything, NaN too: its choice stays an expert
+  }
   __syncwarp();
   if (groups > 1) {
     const int per = experts / groups;
@@ -105,10 +105,85 @@ moe_route_kernel(const float* __restrict__ logits, int tokens, int experts, int 
   if (renormalise && lane < top) weights[(size_t)t * top + lane] /= total;     // (top <= 32 where this is asked for)
 }
 
+__global__ void __launch_bounds__(kRouteWarps * 32)
+moe_route_kernel(const float* __restrict__ logits, int tokens, int experts, int top, int groups, int keep,
+                 int renormalise, int* __restrict__ ids, float* __restrict__ weights) {
+  extern __shared__ float route_smem[];       // per warp: scores[experts], group scores[groups]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * kRouteWarps + warp;
+  grid_dependency_wait();
+  if (t >= tokens) return;
+  float* sc = route_smem + warp * (experts + groups);
+  route_token(logits + (size_t)t * experts, sc, sc + experts, lane, t, experts, top, groups, keep, renormalise, ids,
+              weights);
+}
+
+// The router's product and the routing in one launch: logits[e] = sum_k x[k] * w[e][k] in 32-bit (lane l adds up
+// k = l, l + 32, ..., then the lanes' sums meet in a fixed tree: the same bits whatever else is in the step), then
+// `route_token`.  A block takes TOK tokens; its warps take the experts in turn.
+constexpr int kRouterWarps = 8;
+
+template <typename T, int TOK>
+__global__ void __launch_bounds__(kRouterWarps * 32)
+moe_router_kernel(const T* __restrict__ x, size_t x_stride, const float* __restrict__ w, int tokens, int K, int experts,
+                  int top, int groups, int keep, int renormalise, int* __restrict__ ids, float* __restrict__ weights) {
+  extern __shared__ float route_smem[];       // TOK x (logits[experts], group scores[groups])
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t0 = blockIdx.x * TOK;
+  grid_dependency_wait();
+  // Four k a lane and round where the rows allow 16-byte reads (several rounds' loads are in flight at once), else one.
+  const bool wide = (K % 4) == 0 && (x_stride % 4) == 0 && aligned16(w) && (reinterpret_cast<uintptr_t>(x) % (4 * sizeof(T))) == 0;
+  for (int e = warp; e < experts; e += kRouterWarps) {
+    const float* we = w + (size_t)e * K;
+    float acc[TOK];
+#pragma unroll
+    for (int t = 0; t < TOK; ++t) acc[t] = 0.f;
+    if (wide) {
+#pragma unroll 4
+      for (int k = lane * 4; k < K; k += 128) {
+        const float4 wv = *reinterpret_cast<const float4*>(we + k);
+#pragma unroll
+        for (int t = 0; t < TOK; ++t) {
+          if (t0 + t >= tokens) continue;
+          const T* xr = x + (size_t)(t0 + t) * x_stride + k;
+          float x0, x1, x2, x3;
+          if (sizeof(T) == 4) {
+            const float4 xv = *reinterpret_cast<const float4*>(xr);
+            x0 = xv.x; x1 = xv.y; x2 = xv.z; x3 = xv.w;
+          } else {
+            const uint2 xv = *reinterpret_cast<const uint2*>(xr);
+            x0 = __uint_as_float(xv.x << 16); x1 = __uint_as_float(xv.x & 0xffff0000u);
+            x2 = __uint_as_float(xv.y << 16); x3 = __uint_as_float(xv.y & 0xffff0000u);
+          }
+          acc[t] = fmaf(x3, wv.w, fmaf(x2, wv.z, fmaf(x1, wv.y, fmaf(x0, wv.x, acc[t]))));
+        }
+      }
+    } else {
+      for (int k = lane; k < K; k += 32) {
+        const float wv = we[k];
+#pragma unroll
+        for (int t = 0; t < TOK; ++t)
+          if (t0 + t < tokens) acc[t] = fmaf(to_float(x[(size_t)(t0 + t) * x_stride + k]), wv, acc[t]);
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < TOK; ++t) {
+      const float sum = warp_sum(acc[t]);
+      if (lane == 0) route_smem[t * (experts + groups) + e] = sum;
+    }
+  }
+  __syncthreads();
+  if (warp < TOK && t0 + warp < tokens) {
+    float* sc = route_smem + warp * (experts + groups);
+    route_token(sc, sc, sc + experts, lane, t0 + warp, experts, top, groups, keep, renormalise, ids, weights);
+  }
+}
+
 // ------------------------------------------------------------------------------------------- sort
 __global__ void __launch_bounds__(1024)
 moe_sort_kernel(const int* __restrict__ ids, int pairs, int experts, int tile_rows, int* __restrict__ offsets,
-                int* __restrict__ order, int* __restrict__ tile_expert, int* __restrict__ tile_row0, int max_tiles) {
+                int* __restrict__ order, int* __restrict__ tile_expert, int* __restrict__ tile_row0, int max_tiles,
+                int* __restrict__ place) {
   extern __shared__ int sort_smem[];          // counts[experts], cursor[experts]
   int* counts = sort_smem;
   int* cursor = sort_smem + experts;
@@ -139,12 +214,36 @@ moe_sort_kernel(const int* __restrict__ ids, int pairs, int experts, int tile_ro
   // The order of an expert's rows among themselves does not matter: every row of the products is computed alone.
   for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
     const int e = ids[i];
-    if (e >= 0 && e < experts) order[atomicAdd(&cursor[e], 1)] = i;
+    if (e >= 0 && e < experts) {
+      const int at = atomicAdd(&cursor[e], 1);
+      order[at] = i;
+      if (place != nullptr) place[i] = at;
+    }
+  }
+}
+
+// out[m] = x[order[m] / top]: every pair's token row, in the order of the experts' runs.
+template <typename T>
+__global__ void moe_gather_kernel(const T* __restrict__ x, size_t x_stride, const int* __restrict__ order, int top,
+                                  T* __restrict__ out, int pairs, int width) {
+  constexpr int N = Vec16<T>::N;
+  grid_dependency_wait();
+  const int per_row = width / N;
+  const size_t total = (size_t)pairs * per_row;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int m = (int)(i / per_row), c = (int)(i - (size_t)m * per_row) * N;
+    store16(out + (size_t)m * width + c, load16(x + (size_t)(order[m] / top) * x_stride + c));
   }
 }
 
 // --------------------------------------------------------------------------------- grouped, FFMA
 constexpr int kSimtRows = 32;       // rows of a tile
+
+// The row of an expert's [2N, K] matrix that holds column `col` of the gate (or of the up) product: the gate rows,
+// then the up rows; or, `eights`, both interleaved in eights (eight gate rows, then their eight up rows).
+__device__ __forceinline__ int gate_up_row(int col, bool up, int N, int eights) {
+  return eights ? (col >> 3) * 16 + (up ? 8 : 0) + (col & 7) : (up ? N : 0) + col;
+}
 
 // a: rows of `a_stride`; w: [experts][rows of W][K] with rows of W = 2N (gate rows, then up rows) or N (down).
 // A block: one tile of rows of one expert x 64 rows of W (gate/up: 32 of each for the same 32 columns).
@@ -154,7 +253,7 @@ moe_grouped_simt_kernel(const T* __restrict__ a, size_t a_stride, const T* __res
                         size_t out_stride, const int* __restrict__ order, const int* __restrict__ offsets,
                         const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
                         const float* __restrict__ pair_weights, int top, int N, int K, int act, float limit,
-                        float alpha) {
+                        float alpha, int eights) {
   __shared__ float As[kSimtRows][33];
   __shared__ float Bs[64][33];
   __shared__ int src_rows[kSimtRows], out_rows[kSimtRows];
@@ -183,7 +282,7 @@ moe_grouped_simt_kernel(const T* __restrict__ a, size_t a_stride, const T* __res
       const int r = i >> 5, c = i & 31;
       int wrow;
       bool ok;
-      if (MODE == kModeGateUp) { ok = n0 + (r & 31) < N; wrow = (r < 32 ? 0 : N) + n0 + (r & 31); }
+      if (MODE == kModeGateUp) { ok = n0 + (r & 31) < N; wrow = gate_up_row(n0 + (r & 31), r >= 32, N, eights); }
       else { ok = n0 + r < N; wrow = n0 + r; }
       Bs[r][c] = (ok && k0 + c < K) ? to_float(we[(size_t)wrow * K + k0 + c]) : 0.f;
     }
@@ -230,7 +329,7 @@ moe_grouped_mma_kernel(const bf16* __restrict__ a, size_t a_stride, const bf16* 
                        size_t out_stride, const int* __restrict__ order, const int* __restrict__ offsets,
                        const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
                        const float* __restrict__ pair_weights, int top, int N, int K, int act, float limit,
-                       float alpha) {
+                       float alpha, int eights) {
   __shared__ __align__(16) bf16 As[2][kMmaRows * kMmaLd];
   __shared__ __align__(16) bf16 Bs[2][64 * kMmaLd];
   __shared__ int src_rows[kMmaRows], out_rows[kMmaRows];
@@ -262,7 +361,7 @@ moe_grouped_mma_kernel(const bf16* __restrict__ a, size_t a_stride, const bf16* 
       const int idx = tid + i * 128, r = idx >> 3, c = idx & 7, k = k0 + c * 8;
       int wrow;
       bool ok;
-      if (MODE == kModeGateUp) { ok = n0 + (r & 31) < N; wrow = (r < 32 ? 0 : N) + n0 + (r & 31); }
+      if (MODE == kModeGateUp) { ok = n0 + (r & 31) < N; wrow = gate_up_row(n0 + (r & 31), r >= 32, N, eights); }
       else { ok = n0 + r < N; wrow = n0 + r; }
       const bool valid = ok && k < K;
       cp_async16(&Bs[buf][r * kMmaLd + c * 8], valid ? we + (size_t)wrow * K + k : we, valid);
@@ -329,13 +428,17 @@ moe_grouped_mma_kernel(const bf16* __restrict__ a, size_t a_stride, const bf16* 
 
 // ---------------------------------------------------------------------------------------- combine
 template <typename T>
-__global__ void moe_combine_kernel(const T* __restrict__ y, T* __restrict__ out, size_t tokens, int top, int width) {
+__global__ void moe_combine_kernel(const T* __restrict__ y, T* __restrict__ out, size_t tokens, int top, int width,
+                                   const int* __restrict__ place) {
   grid_dependency_wait();
   const size_t total = tokens * width;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const size_t t = i / width, c = i - t * width;
     float sum = 0.f;
-    for (int s = 0; s < top; ++s) sum += to_float(y[(t * top + s) * width + c]);
+    for (int s = 0; s < top; ++s) {
+      const size_t row = place != nullptr ? (size_t)place[t * top + s] : t * top + s;
+      sum += to_float(y[row * width + c]);
+    }
     out[i] = from_float<T>(sum);
   }
 }
@@ -343,21 +446,23 @@ __global__ void moe_combine_kernel(const T* __restrict__ y, T* __restrict__ out,
 template <typename T, int MODE>
 static int launch_simt(const void* a, size_t a_stride, const void* w, void* out, size_t out_stride, const int* order,
                        const int* offsets, const int* tile_expert, const int* tile_row0, const float* pair_weights,
-                       int top, int N, int K, int act, float limit, float alpha, int max_tiles, cudaStream_t stream) {
+                       int top, int N, int K, int act, float limit, float alpha, int max_tiles, int eights,
+                       cudaStream_t stream) {
   const dim3 grid(max_tiles, MODE == kModeGateUp ? (N + 31) / 32 : (N + 63) / 64);
   return (int)launch_pdl(max_tiles, moe_grouped_simt_kernel<T, MODE>, grid, dim3(256), 0, stream, (const T*)a, a_stride,
                          (const T*)w, (T*)out, out_stride, order, offsets, tile_expert, tile_row0, pair_weights, top, N,
-                         K, act, limit, alpha);
+                         K, act, limit, alpha, eights);
 }
 
 template <int MODE>
 static int launch_mma(const void* a, size_t a_stride, const void* w, void* out, size_t out_stride, const int* order,
                       const int* offsets, const int* tile_expert, const int* tile_row0, const float* pair_weights,
-                      int top, int N, int K, int act, float limit, float alpha, int max_tiles, cudaStream_t stream) {
+                      int top, int N, int K, int act, float limit, float alpha, int max_tiles, int eights,
+                      cudaStream_t stream) {
   const dim3 grid(max_tiles, MODE == kModeGateUp ? (N + 31) / 32 : (N + 63) / 64);
   return (int)launch_pdl(max_tiles, moe_grouped_mma_kernel<MODE>, grid, dim3(128), 0, stream, (const bf16*)a, a_stride,
                          (const bf16*)w, (bf16*)out, out_stride, order, offsets, tile_expert, tile_row0, pair_weights,
-                         top, N, K, act, limit, alpha);
+                         top, N, K, act, limit, alpha, eights);
 }
 
 }  // namespace li
@@ -384,14 +489,52 @@ LI_EXPORT int li_moe_tile_rows(int dtype, int N, int K) {
 
 // ids [pairs] int (the expert of every pair); offsets [experts + 1]; order [pairs]; tile_expert, tile_row0 [max_tiles]
 // with max_tiles >= pairs / tile_rows + experts.
+// place [pairs] (optional): where in `order` each pair stands.
 LI_EXPORT int li_moe_sort(const int* ids, int pairs, int experts, int tile_rows, int* offsets, int* order,
-                          int* tile_expert, int* tile_row0, int max_tiles, cudaStream_t stream) {
+                          int* tile_expert, int* tile_row0, int max_tiles, int* place, cudaStream_t stream) {
   if (experts < 1 || tile_rows < 1 || max_tiles < (pairs + tile_rows - 1) / tile_rows + experts - 1)
     return LI_ERR_UNSUPPORTED;
   const size_t smem = (size_t)2 * experts * sizeof(int);
   if (smem > 48 * 1024) return LI_ERR_UNSUPPORTED;
   return (int)launch_pdl(pairs, moe_sort_kernel, dim3(1), dim3(1024), smem, stream, ids, pairs, experts, tile_rows,
-                         offsets, order, tile_expert, tile_row0, max_tiles);
+                         offsets, order, tile_expert, tile_row0, max_tiles, place);
+}
+
+// x [tokens, K] (rows x_stride apart) in the engine's dtype, w [experts, K] float: the router's product and the routing
+// of li_moe_route in one launch.
+LI_EXPORT int li_moe_router(int dtype, const void* x, size_t x_stride, const float* w, int tokens, int K, int experts,
+                            int top, int groups, int keep, int renormalise, int* ids, float* weights,
+                            cudaStream_t stream) {
+  if (tokens == 0) return 0;
+  if (experts < 1 || top < 1 || top > experts || groups < 1 || experts % groups || keep < 1 || keep > groups || K < 1)
+    return LI_ERR_UNSUPPORTED;
+  if (keep * (experts / groups) < top || (renormalise && top > 32)) return LI_ERR_UNSUPPORTED;
+  const bool wide = tokens > 128;
+  const size_t smem = (size_t)(wide ? 8 : 1) * (experts + groups) * sizeof(float);
+  if (smem > 48 * 1024) return LI_ERR_UNSUPPORTED;
+#define LI_ROUTER(T, TOK)                                                                                             \
+  return (int)launch_pdl(tokens, moe_router_kernel<T, TOK>, dim3((tokens + TOK - 1) / TOK), dim3(kRouterWarps * 32),   \
+                         smem, stream, (const T*)x, x_stride, w, tokens, K, experts, top, groups, keep, renormalise,  \
+                         ids, weights)
+  if (dtype == kFloat32) { if (wide) LI_ROUTER(float, 8); LI_ROUTER(float, 1); }
+  if (wide) LI_ROUTER(bf16, 8);
+  LI_ROUTER(bf16, 1);
+#undef LI_ROUTER
+}
+
+// out [pairs, width] = x[order[m] / top] for every place m of `order`; width a multiple of 16 bytes.
+LI_EXPORT int li_moe_gather(int dtype, const void* x, size_t x_stride, const int* order, int top, void* out, int pairs,
+                            int width, cudaStream_t stream) {
+  if (pairs == 0 || width == 0) return 0;
+  const int n = dtype == kFloat32 ? 4 : 8;
+  if (width % n || x_stride % n || !aligned16(x) || !aligned16(out)) return LI_ERR_ALIGNMENT;
+  const size_t total = (size_t)pairs * (width / n);
+  const dim3 grid((unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16));
+  if (dtype == kFloat32)
+    return (int)launch_pdl(pairs, moe_gather_kernel<float>, grid, dim3(256), 0, stream, (const float*)x, x_stride, order,
+                           top, (float*)out, pairs, width);
+  return (int)launch_pdl(pairs, moe_gather_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16*)x, x_stride, order, top,
+                         (bf16*)out, pairs, width);
 }
 
 // mode 0: out[pair, 0:N] = act(W_gate,e x[pair / top], W_up,e x[pair / top]), w [experts, 2N, K] (gate rows, then up).
@@ -401,14 +544,16 @@ LI_EXPORT int li_moe_sort(const int* ids, int pairs, int experts, int tile_rows,
 LI_EXPORT int li_moe_grouped(int dtype, int mode, const void* a, size_t a_stride, const void* w, void* out,
                              size_t out_stride, const int* order, const int* offsets, const int* tile_expert,
                              const int* tile_row0, const float* pair_weights, int top, int N, int K, int act,
-                             float limit, float alpha, int max_tiles, int tile_rows, cudaStream_t stream) {
+                             float limit, float alpha, int max_tiles, int tile_rows, int eights,
+                             cudaStream_t stream) {
   if (max_tiles <= 0 || N <= 0 || K <= 0) return 0;
   if (tile_rows != kSimtRows && !(tile_rows == kMmaRows && li_moe_tile_rows(dtype, N, K) == kMmaRows))
     return LI_ERR_UNSUPPORTED;
   if (mode != kModeGateUp && mode != kModeDown) return LI_ERR_UNSUPPORTED;
+  if (eights && mode == kModeGateUp && (N % 8)) return LI_ERR_UNSUPPORTED;
   if (max_tiles > 0x7fffffff / 2 || (N + 31) / 32 > 65535) return LI_ERR_UNSUPPORTED;
 #define LI_MOE_ARGS a, a_stride, w, out, out_stride, order, offsets, tile_expert, tile_row0, pair_weights, top, N, K, act, \
-                    limit, alpha, max_tiles, stream
+                    limit, alpha, max_tiles, eights, stream
   if (dtype == kFloat32)
     return mode == kModeGateUp ? launch_simt<float, kModeGateUp>(LI_MOE_ARGS) : launch_simt<float, kModeDown>(LI_MOE_ARGS);
   if (tile_rows == kMmaRows) {
@@ -420,14 +565,16 @@ LI_EXPORT int li_moe_grouped(int dtype, int mode, const void* a, size_t a_stride
 #undef LI_MOE_ARGS
 }
 
-// out [tokens, width] = sum over s < top of y[token * top + s, :], in slot order.
-LI_EXPORT int li_moe_combine(int dtype, const void* y, void* out, int tokens, int top, int width, cudaStream_t stream) {
+// out [tokens, width] = sum over s < top of y[row of pair token * top + s, :], in slot order; the row is the pair
+// itself, or place[pair] where `place` is given (rows in the order of the experts' runs).
+LI_EXPORT int li_moe_combine(int dtype, const void* y, void* out, int tokens, int top, int width, const int* place,
+                             cudaStream_t stream) {
   const size_t total = (size_t)tokens * width;
   if (total == 0) return 0;
   const dim3 grid((unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16));
   if (dtype == kFloat32)
     return (int)launch_pdl(tokens, moe_combine_kernel<float>, grid, dim3(256), 0, stream, (const float*)y, (float*)out,
-                           (size_t)tokens, top, width);
+                           (size_t)tokens, top, width, place);
   return (int)launch_pdl(tokens, moe_combine_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16*)y, (bf16*)out,
-                         (size_t)tokens, top, width);
+                         (size_t)tokens, top, width, place);
 }

@@ -55,11 +55,18 @@ _SIGNATURES = {
     "li_softcap": ("elementwise", [c_int, c_void_p, c_size_t, c_float, c_void_p]),
     "li_moe_route": ("moe", [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "li_moe_tile_rows": ("moe", [c_int, c_int, c_int]),
-    "li_moe_sort": ("moe", [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+    "li_moe_sort": ("moe", [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                            c_void_p]),
+    "li_moe_router": ("moe", [c_int, c_void_p, c_size_t, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                              c_void_p, c_void_p, c_void_p]),
+    "li_moe_gather": ("moe", [c_int, c_void_p, c_size_t, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]),
+    "li_gemm_tcgen05_grouped": ("gemm_tcgen05", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                                                 c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                                 c_void_p, c_void_p]),
     "li_moe_grouped": ("moe", [c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p,
                                c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_int,
-                               c_int, c_void_p]),
-    "li_moe_combine": ("moe", [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+                               c_int, c_int, c_void_p]),
+    "li_moe_combine": ("moe", [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "li_sigmoid_gate_heads": ("rope_cache", [c_int, c_void_p, c_void_p, c_size_t, c_int, c_int, c_int, c_void_p]),
     "li_mlstm": ("mlstm", [c_int, c_void_p, c_size_t, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
                            c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
@@ -1465,6 +1472,7 @@ class ExpertPlan:
     tile_row0: torch.Tensor     # [max_tiles] int32: its first row in `order`
     tile_rows: int
     max_tiles: int
+    place: torch.Tensor | None = None   # [pairs] int32: where in `order` each pair stands
 
 
 def moe_route(logits: torch.Tensor, top: int, groups: int, keep: int, renormalise: bool, ids: torch.Tensor,
@@ -1482,38 +1490,102 @@ def moe_route(logits: torch.Tensor, top: int, groups: int, keep: int, renormalis
                                weights.data_ptr(), _stream()), "moe_route")
 
 
-def moe_tile_rows(dtype: torch.dtype, hidden: int, ff: int) -> int:
-    """Rows of a tile of `moe_grouped`: 64 where both of an expert's products run on tensor cores, else 32."""
+def moe_router(x: torch.Tensor, weight: torch.Tensor, top: int, groups: int, keep: int, renormalise: bool,
+               ids: torch.Tensor, weights: torch.Tensor) -> None:
+    """`moe_route` of the logits x @ weight^T, product and routing in one launch: x [tokens, hidden] in the engine's
+    dtype (a column slice is fine), weight [experts, hidden] float32; the product is 32-bit, its sums in an order that
+    depends on nothing but the sizes."""
+    _on_gpu(weight, ids, weights)
+    _rows2d(x, "x")
+    _int32(ids, "ids")
+    tokens, hidden = x.shape
+    experts = weight.shape[0]
+    assert weight.dtype == torch.float32 == weights.dtype and weight.shape == (experts, hidden)
+    assert ids.shape == weights.shape == (tokens, top) and ids.is_contiguous() and weights.is_contiguous()
+    _check(_fn("li_moe_router")(_code(x), x.data_ptr(), x.stride(0), weight.data_ptr(), tokens, hidden, experts, top,
+                                groups, keep, int(renormalise), ids.data_ptr(), weights.data_ptr(), _stream()),
+           "moe_router")
+
+
+# LITEINFER_MOE_TCGEN05: 1 (default) = bfloat16 experts of steps with at least LITEINFER_MOE_TCGEN05_MIN_PAIRS (1) pairs of
+# (token, expert) run their products on the tcgen05 kernel; 0 = every step on the mma.sync tiles (measured on B200 at
+# width 2,048 with 32 experts 2,048 wide, four a token: 2,048 tokens 350 against 958 us, 64 tokens 158 against 222, 8
+# tokens 124 against 164).
+MOE_TCGEN05 = os.environ.get("LITEINFER_MOE_TCGEN05", "1") != "0"
+MOE_TCGEN05_MIN_PAIRS = int(os.environ.get("LITEINFER_MOE_TCGEN05_MIN_PAIRS", "1"))
+
+
+def moe_tile_rows(dtype: torch.dtype, hidden: int, ff: int, pairs: int | None = None) -> int:
+    """Rows of a tile of an expert's products: 128 where the tcgen05 kernel takes them (bfloat16, sizes in eights, a
+    step of many pairs), 64 where both run on mma.sync tiles, else 32 (FFMA tiles)."""
     if not torch.cuda.is_available():
         return 32
     code = _DTYPE_CODE[dtype]
     both = _fn("li_moe_tile_rows")(code, ff, hidden) == 64 and _fn("li_moe_tile_rows")(code, hidden, ff) == 64
+    if both and pairs is not None and MOE_TCGEN05 and pairs >= MOE_TCGEN05_MIN_PAIRS and hidden % 8 == 0 and ff % 8 == 0:
+        return 128
     return 64 if both else 32
 
 
-def moe_sort(ids: torch.Tensor, experts: int, tile_rows: int) -> ExpertPlan:
+def moe_sort(ids: torch.Tensor, experts: int, tile_rows: int, with_place: bool = False) -> ExpertPlan:
     """The plan of a step whose pair p = token * top + slot goes to expert ids.flatten()[p]."""
     _on_gpu(ids)
     _int32(ids, "ids")
     pairs = ids.numel()
     max_tiles = -(-pairs // tile_rows) + experts
-    scratch = torch.empty(pairs + experts + 1 + 2 * max_tiles, dtype=torch.int32, device=ids.device)
+    scratch = torch.empty(pairs * (2 if with_place else 1) + experts + 1 + 2 * max_tiles, dtype=torch.int32,
+                          device=ids.device)
     order, offsets = scratch[:pairs], scratch[pairs:pairs + experts + 1]
     tile_expert = scratch[pairs + experts + 1:pairs + experts + 1 + max_tiles]
-    tile_row0 = scratch[pairs + experts + 1 + max_tiles:]
+    tile_row0 = scratch[pairs + experts + 1 + max_tiles:pairs + experts + 1 + 2 * max_tiles]
+    place = scratch[pairs + experts + 1 + 2 * max_tiles:] if with_place else None
     _check(_fn("li_moe_sort")(ids.data_ptr(), pairs, experts, tile_rows, offsets.data_ptr(), order.data_ptr(),
-                              tile_expert.data_ptr(), tile_row0.data_ptr(), max_tiles, _stream()), "moe_sort")
-    return ExpertPlan(order, offsets, tile_expert, tile_row0, tile_rows, max_tiles)
+                              tile_expert.data_ptr(), tile_row0.data_ptr(), max_tiles, _ptr(place), _stream()),
+           "moe_sort")
+    return ExpertPlan(order, offsets, tile_expert, tile_row0, tile_rows, max_tiles, place)
+
+
+def moe_gather(x: torch.Tensor, plan: ExpertPlan, top: int, out: torch.Tensor) -> torch.Tensor:
+    """out[m] = x[plan.order[m] // top]: every pair's token row, in the order of the experts' runs."""
+    _on_gpu(out)
+    _rows2d(x, "x")
+    pairs = plan.order.numel()
+    assert out.shape == (pairs, x.shape[1]) and out.dtype == x.dtype and out.is_contiguous()
+    _check(_fn("li_moe_gather")(_code(x), x.data_ptr(), x.stride(0), plan.order.data_ptr(), top, out.data_ptr(), pairs,
+                                x.shape[1], _stream()), "moe_gather")
+    return out
+
+
+def moe_grouped_tcgen05(mode: str, a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, plan: ExpertPlan,
+                        activation: str = "swiglu", limit: float = 0.0, alpha: float = 1.0,
+                        pair_weights: torch.Tensor | None = None) -> torch.Tensor:
+    """`moe_grouped` on the tcgen05 kernel (bfloat16): `a` [pairs, K] and `out` hold their rows in the order of the
+    experts' runs (`plan.order`), the plan's tiles are 128 rows, and in mode "gate_up" an expert's gate and up rows lie
+    interleaved in eights.  mode "down" multiplies row m by pair_weights[plan.order[m]]."""
+    _on_gpu(a, weight, out, pair_weights)
+    experts, rows, K = weight.shape
+    pairs = plan.order.numel()
+    assert plan.tile_rows == 128 and mode in ("gate_up", "down") and a.dtype == weight.dtype == out.dtype == torch.bfloat16
+    assert a.shape == (pairs, K) and out.shape == (pairs, rows // 2 if mode == "gate_up" else rows)
+    act = -1 if mode == "down" else {"swiglu": 0, "capped_swiglu": 4}[activation]
+    scale = pair_weights if mode == "down" else None
+    _check(_fn("li_gemm_tcgen05_grouped")(
+        a.data_ptr(), weight.data_ptr(), out.data_ptr(), pairs, rows, K, experts, act, float(limit), float(alpha),
+        plan.tile_expert.data_ptr(), plan.tile_row0.data_ptr(), plan.offsets.data_ptr(), plan.max_tiles,
+        plan.order.data_ptr() if scale is not None else None, _ptr(scale),
+        scratch_for(a.device).gemm_error.data_ptr(), _stream()), "gemm_tcgen05_grouped")
+    return out
 
 
 def moe_grouped(mode: str, a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, plan: ExpertPlan, top: int,
                 activation: str = "swiglu", limit: float = 0.0, alpha: float = 1.0,
-                pair_weights: torch.Tensor | None = None) -> torch.Tensor:
+                pair_weights: torch.Tensor | None = None, eights: bool = False) -> torch.Tensor:
     """The experts' products, grouped by expert.  mode "gate_up": out[p] = act(W_gate,e a[p // top], W_up,e a[p // top])
     for pair p of expert e; a [tokens, hidden], weight [experts, 2 * ff, hidden] (an expert's gate rows, then its up
     rows), out [pairs, ff]; `activation` of `EXPERT_ACTIVATIONS` ("capped_swiglu": g' = min(g, limit), u' = clamp(u,
     -limit, limit), g' * sigmoid(alpha * g') * (u' + 1)).  mode "down": out[p] = (W_down,e a[p]) * pair_weights[p];
-    a [pairs, ff], weight [experts, hidden, ff], out [pairs, hidden]."""
+    a [pairs, ff], weight [experts, hidden, ff], out [pairs, hidden].  `eights` (mode "gate_up"): an expert's gate and
+    up rows lie interleaved in eights (eight gate rows, then their eight up rows) instead of one half after the other."""
     _on_gpu(a, weight, out, pair_weights)
     _rows2d(a, "a")
     assert mode in ("gate_up", "down") and a.dtype == weight.dtype == out.dtype and out.is_contiguous()
@@ -1525,17 +1597,43 @@ def moe_grouped(mode: str, a: torch.Tensor, weight: torch.Tensor, out: torch.Ten
                                  out.data_ptr(), out.stride(0), plan.order.data_ptr(), plan.offsets.data_ptr(),
                                  plan.tile_expert.data_ptr(), plan.tile_row0.data_ptr(), _ptr(pair_weights), top, N, K,
                                  EXPERT_ACTIVATIONS[activation], float(limit), float(alpha), plan.max_tiles,
-                                 plan.tile_rows, _stream()), "moe_grouped")
+                                 plan.tile_rows, int(eights), _stream()), "moe_grouped")
     return out
 
 
-def moe_combine(y: torch.Tensor, out: torch.Tensor, top: int) -> torch.Tensor:
-    """out[t] = sum over s < top of y[t * top + s], in slot order, summed in 32-bit."""
-    _on_gpu(y, out)
+def moe_combine(y: torch.Tensor, out: torch.Tensor, top: int, place: torch.Tensor | None = None) -> torch.Tensor:
+    """out[t] = sum over s < top of y[t * top + s], in slot order, summed in 32-bit; with `place` the row of pair p is
+    y[place[p]] (rows in the order of the experts' runs)."""
+    _on_gpu(y, out, place)
     tokens, width = out.shape
     assert y.shape == (tokens * top, width) and y.dtype == out.dtype and y.is_contiguous() and out.is_contiguous()
-    _check(_fn("li_moe_combine")(_code(y), y.data_ptr(), out.data_ptr(), tokens, top, width, _stream()), "moe_combine")
+    _check(_fn("li_moe_combine")(_code(y), y.data_ptr(), out.data_ptr(), tokens, top, width, _ptr(place), _stream()),
+           "moe_combine")
     return out
+
+
+def moe_experts(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
+                activation: str, limit: float, alpha: float, eights: bool, out: torch.Tensor) -> torch.Tensor:
+    """out[t] = sum_s weights[t, s] * down_e(act(gate_e x[t], up_e x[t])), e = ids[t, s]: the chosen experts of every
+    token, their products grouped by expert.  gate_up [experts, 2 * ff, hidden] (`eights`: gate and up rows interleaved
+    in eights), down [experts, hidden, ff].  Steps of many pairs in bfloat16 run the tcgen05 kernel over the pairs'
+    rows gathered expert by expert; the others the mma.sync or FFMA tiles, which gather as they load."""
+    tokens, top = ids.shape
+    experts, hidden, ff = down.shape
+    pairs = tokens * top
+    tile = moe_tile_rows(x.dtype, hidden, ff, pairs if eights else None)
+    plan = moe_sort(ids, experts, tile, with_place=tile == 128)
+    act = torch.empty((pairs, ff), dtype=x.dtype, device=x.device)
+    each = torch.empty((pairs, hidden), dtype=x.dtype, device=x.device)
+    scale = weights.view(-1)
+    if tile == 128:
+        rows = moe_gather(x, plan, top, torch.empty((pairs, hidden), dtype=x.dtype, device=x.device))
+        moe_grouped_tcgen05("gate_up", rows, gate_up, act, plan, activation, limit, alpha)
+        moe_grouped_tcgen05("down", act, down, each, plan, pair_weights=scale)
+        return moe_combine(each, out, top, place=plan.place)
+    moe_grouped("gate_up", x, gate_up, act, plan, top, activation, limit, alpha, eights=eights)
+    moe_grouped("down", act, down, each, plan, top, pair_weights=scale)
+    return moe_combine(each, out, top)
 
 
 # ------------------------------------------------------------------ sampling

@@ -127,7 +127,7 @@ class RoutedExperts:
         self.limit, self.alpha, self.renormalise = float(limit), float(alpha), bool(renormalise)
         self.dtype, self.device = dtype, device
         self.router = self.gate_up = self.down = None
-        self.tile_rows = 32
+        self.eights = False
 
     def tensor_specs(self) -> dict[str, TensorSpec]:
         f, h = self.intermediate_size, self.hidden_size
@@ -140,32 +140,32 @@ class RoutedExperts:
 
     def bind(self, tensors: dict[str, torch.Tensor]) -> None:
         self.router = tensors["router.weight"].to(torch.float32).contiguous()
-        # [experts, 2 * ff, hidden]: an expert's gate rows, then its up rows; [experts, hidden, ff].
-        self.gate_up = torch.stack([torch.cat([tensors[f"experts.{e}.gate_proj.weight"],
-                                               tensors[f"experts.{e}.up_proj.weight"]]) for e in range(self.experts)])
-        self.down = torch.stack([tensors[f"experts.{e}.down_proj.weight"] for e in range(self.experts)])
-        self.tile_rows = ops.moe_tile_rows(self.gate_up.dtype, self.hidden_size, self.intermediate_size)
+        # [experts, 2 * ff, hidden]: an expert's gate rows, then its up rows; in bfloat16 with a width in eights both
+        # interleaved in eights (eight gate rows, then their eight up rows), the layout whose product and activation
+        # the tensor-core kernels do together.  [experts, hidden, ff].
+        gates = [tensors[f"experts.{e}.gate_proj.weight"] for e in range(self.experts)]
+        ups = [tensors[f"experts.{e}.up_proj.weight"] for e in range(self.experts)]
+        self.eights = gates[0].dtype == torch.bfloat16 and self.intermediate_size % 8 == 0
+        if self.eights:
+            pair = lambda g, u: torch.stack([g.unflatten(0, (-1, 8)), u.unflatten(0, (-1, 8))], dim=1).flatten(0, 2)
+        else:
+            pair = lambda g, u: torch.cat([g, u])
+        self.gate_up = torch.stack([pair(g, u) for g, u in zip(gates, ups)]).contiguous()
+        self.down = torch.stack([tensors[f"experts.{e}.down_proj.weight"] for e in range(self.experts)]).contiguous()
 
     def route(self, x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
         """(chosen experts [tokens, top] int32, their weights [tokens, top] float32)."""
         tokens = x.shape[0]
-        wide = x if x.dtype == torch.float32 else ops.convert(
-            x, torch.empty(x.shape, dtype=torch.float32, device=x.device))
-        logits = ops.linear(wide, self.router, None)
         ids = torch.empty((tokens, self.top), dtype=torch.int32, device=x.device)
         weights = torch.empty((tokens, self.top), dtype=torch.float32, device=x.device)
-        ops.moe_route(logits, self.top, self.groups, self.groups_keep, self.renormalise, ids, weights)
+        ops.moe_router(x, self.router, self.top, self.groups, self.groups_keep, self.renormalise, ids, weights)
         return ids, weights
 
     def forward(self, x, ctx: StepContext):
-        tokens, pairs = x.shape[0], x.shape[0] * self.top
         ids, weights = self.route(x)
-        plan = ops.moe_sort(ids, self.experts, self.tile_rows)
-        hidden = torch.empty((pairs, self.intermediate_size), dtype=x.dtype, device=x.device)
-        ops.moe_grouped("gate_up", x, self.gate_up, hidden, plan, self.top, self.activation, self.limit, self.alpha)
-        each = torch.empty((pairs, self.hidden_size), dtype=x.dtype, device=x.device)
-        ops.moe_grouped("down", hidden, self.down, each, plan, self.top, pair_weights=weights.view(-1))
-        return ops.moe_combine(each, torch.empty((tokens, self.hidden_size), dtype=x.dtype, device=x.device), self.top)
+        out = torch.empty((x.shape[0], self.hidden_size), dtype=x.dtype, device=x.device)
+        return ops.moe_experts(x, self.gate_up, self.down, ids, weights, self.activation, self.limit, self.alpha,
+                               self.eights, out)
 
 
 register_feed_forward("gated_mlp", GatedMLP)

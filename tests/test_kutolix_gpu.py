@@ -298,6 +298,18 @@ def test_router_against_the_plain_mechanism(experts, top, groups, keep, renormal
     assert torch.equal(ids.cpu().long().sort(-1).values, chosen.sort(-1).values)
     torch.testing.assert_close(weights.cpu().double().sort(-1).values, scores.sort(-1).values, rtol=1e-5, atol=1e-6)
     assert torch.equal(ids.cpu().long(), chosen)            # the largest first, as the plain top-k orders them
+    # The router's product and the routing in one launch, in both dtypes and both widths of block, rows of a slice.
+    for dtype in DTYPES:
+        for count in (tokens, 300):
+            wide = _randn(count, 3 + 40 + 2, seed=5, dtype=dtype)
+            x, w = wide[:, 3:43], _randn(experts, 40, seed=6, scale=0.7)
+            ops.moe_route(x.float() @ w.t(), top, groups, keep, renormalise,
+                          want_ids := torch.empty(count, top, dtype=torch.int32, device=DEV), want_w := torch.empty(count, top, device=DEV))
+            got_ids, got_w = torch.empty_like(want_ids), torch.empty_like(want_w)
+            ops.moe_router(x, w, top, groups, keep, renormalise, got_ids, got_w)
+            same = (got_ids == want_ids).all(-1)
+            assert float(same.float().mean()) > 0.97            # (a close call may fall the other way: the sums' order differs)
+            torch.testing.assert_close(got_w[same], want_w[same], rtol=1e-4, atol=1e-6)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -320,6 +332,7 @@ def test_grouped_expert_products(dtype, tokens, hidden, ff, experts, top):
     pairs = tokens * top
     tile = ops.moe_tile_rows(dtype, hidden, ff)
     assert tile == (64 if dtype == torch.bfloat16 and hidden % 8 == 0 and ff % 8 == 0 else 32)
+    assert ops.moe_tile_rows(dtype, hidden, ff, 10) == (128 if tile == 64 else tile)      # a step's pairs: the tcgen05 kernel where it fits
     results = []
     for impl, plan in ((ops, ops.moe_sort(ids, experts, tile)), (ref, ref.moe_sort(ids, experts, tile))):
         act = torch.zeros(pairs, ff, dtype=dtype, device=DEV)
@@ -337,6 +350,60 @@ def test_grouped_expert_products(dtype, tokens, hidden, ff, experts, top):
     plain = ops.moe_grouped("gate_up", x, gate_up, torch.zeros(pairs, ff, dtype=dtype, device=DEV), plan, top, "swiglu")
     want = ref.moe_grouped("gate_up", x, gate_up, torch.zeros(pairs, ff, dtype=dtype, device=DEV), ref.moe_sort(ids, experts, tile), top, "swiglu")
     torch.testing.assert_close(plain.float(), want.float(), **_tol(dtype))
+
+
+@pytest.mark.parametrize("tokens,hidden,ff,experts,top", [(300, 128, 64, 4, 4), (200, 512, 256, 8, 2), (2048, 256, 384, 16, 4),
+                                                           (700, 136, 40, 5, 3), (130, 64, 128, 3, 1)])
+def test_expert_products_on_the_tcgen05_kernel(tokens, hidden, ff, experts, top, monkeypatch):
+    """The whole of `moe_experts` with the pairs' rows gathered expert by expert and both products on the tcgen05
+    kernel (tiles of 128 rows, experts with no row, one row, more than a tile; widths that are no multiple of the
+    kernel's tiles), against the mma.sync tiles and the plain twin."""
+    from liteinfer_b200 import ops
+    from liteinfer_b200.ops import kernels
+
+    dtype = torch.bfloat16
+    x = _randn(tokens, hidden, seed=1, dtype=dtype)
+    gate = _randn(experts, ff, hidden, seed=2, scale=hidden ** -0.5, dtype=dtype)
+    up = _randn(experts, ff, hidden, seed=5, scale=hidden ** -0.5, dtype=dtype)
+    eights = torch.stack([gate.unflatten(1, (-1, 8)), up.unflatten(1, (-1, 8))], dim=2).flatten(1, 3).contiguous()
+    down = _randn(experts, hidden, ff, seed=3, scale=ff ** -0.5, dtype=dtype)
+    g = torch.Generator().manual_seed(4)
+    ids = torch.stack([torch.randperm(experts, generator=g)[:top] for _ in range(tokens)]).to(torch.int32)
+    if top == 1:
+        ids[ids == 1] = 0
+    ids = ids.to(DEV)
+    weights = torch.rand(tokens, top, generator=g).to(DEV)
+    out = lambda: torch.empty(tokens, hidden, dtype=dtype, device=DEV)
+    want = ref.moe_experts(x, eights, down, ids, weights, "capped_swiglu", 1.2, 1.702, True, out())
+    monkeypatch.setattr(kernels, "MOE_TCGEN05_MIN_PAIRS", 1)
+    assert ops.moe_tile_rows(dtype, hidden, ff, tokens * top) == 128
+    got = ops.moe_experts(x, eights, down, ids, weights, "capped_swiglu", 1.2, 1.702, True, out())
+    torch.testing.assert_close(got.float(), want.float(), **_tol(dtype))
+    monkeypatch.setattr(kernels, "MOE_TCGEN05", False)
+    tiles = ops.moe_experts(x, eights, down, ids, weights, "capped_swiglu", 1.2, 1.702, True, out())
+    torch.testing.assert_close(tiles.float(), want.float(), **_tol(dtype))
+    halves = ops.moe_experts(x, torch.cat([gate, up], dim=1).contiguous(), down, ids, weights, "swiglu", 0.0, 1.0, False, out())
+    plain = ref.moe_experts(x, torch.cat([gate, up], dim=1), down, ids, weights, "swiglu", 0.0, 1.0, False, out())
+    torch.testing.assert_close(halves.float(), plain.float(), **_tol(dtype))
+    assert ops.gemm_error_flag(DEV) == 0
+
+
+def test_router_gives_every_row_an_expert_whatever_it_holds():
+    """A row of padding may hold anything (what an attention that found no work left in its output): NaN and
+    infinities still choose experts inside the table, so that nothing behind the router reads out of bounds."""
+    from liteinfer_b200 import ops
+
+    experts, top = 12, 3
+    x = _randn(9, 64, seed=1, dtype=torch.bfloat16)
+    x[2], x[5, 7], x[6] = float("nan"), float("inf"), float("-inf")
+    ids = torch.full((9, top), -7, dtype=torch.int32, device=DEV)
+    weights = torch.empty(9, top, device=DEV)
+    ops.moe_router(x, _randn(experts, 64, seed=2), top, 3, 2, False, ids, weights)
+    assert int(ids.min()) >= 0 and int(ids.max()) < experts
+    logits = _randn(9, experts, seed=3)
+    logits[1], logits[4, 2] = float("nan"), float("inf")
+    ops.moe_route(logits, top, 3, 2, False, ids, weights)
+    assert int(ids.min()) >= 0 and int(ids.max()) < experts
 
 
 def test_expert_rows_do_not_depend_on_the_batch():

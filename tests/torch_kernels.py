@@ -611,7 +611,11 @@ def moe_route(logits, top, groups, keep, renormalise, ids, weights):
     weights.copy_(picked)
 
 
-def moe_tile_rows(dtype, hidden, ff):
+def moe_router(x, weight, top, groups, keep, renormalise, ids, weights):
+    moe_route(x.float() @ weight.float().t(), top, groups, keep, renormalise, ids, weights)
+
+
+def moe_tile_rows(dtype, hidden, ff, pairs=None):
     return 32
 
 
@@ -619,19 +623,39 @@ class _Plan:
     def __init__(self, ids, experts):
         self.ids, self.experts = ids.reshape(-1).long(), experts
         self.order = torch.argsort(self.ids, stable=True)
+        self.place = torch.argsort(self.order)
 
 
-def moe_sort(ids, experts, tile_rows):
+def moe_sort(ids, experts, tile_rows, with_place=False):
     return _Plan(ids, experts)
 
 
-def moe_grouped(mode, a, weight, out, plan, top, activation="swiglu", limit=0.0, alpha=1.0, pair_weights=None):
-    rows = weight.shape[1]
+def _halves(w, eights):
+    """(gate rows, up rows) of one expert's [2 * ff, hidden] matrix."""
+    if not eights:
+        return w[:w.shape[0] // 2], w[w.shape[0] // 2:]
+    blocks = w.unflatten(0, (-1, 2, 8))
+    return blocks[:, 0].flatten(0, 1), blocks[:, 1].flatten(0, 1)
+
+
+def moe_experts(x, gate_up, down, ids, weights, activation, limit, alpha, eights, out):
+    tokens, top = ids.shape
+    plan = moe_sort(ids, gate_up.shape[0], 32)
+    act = torch.empty(tokens * top, down.shape[2], dtype=x.dtype, device=x.device)
+    each = torch.empty(tokens * top, down.shape[1], dtype=x.dtype, device=x.device)
+    moe_grouped("gate_up", x, gate_up, act, plan, top, activation, limit, alpha, eights=eights)
+    moe_grouped("down", act, down, each, plan, top, pair_weights=weights.view(-1))
+    return moe_combine(each, out, top)
+
+
+def moe_grouped(mode, a, weight, out, plan, top, activation="swiglu", limit=0.0, alpha=1.0, pair_weights=None,
+                eights=False):
     for pair, e in enumerate(plan.ids.tolist()):
         w = weight[e].float()
         if mode == "gate_up":
             x = a[pair // top].float()
-            g, u = w[:rows // 2] @ x, w[rows // 2:] @ x
+            gate, up = _halves(w, eights)
+            g, u = gate @ x, up @ x
             if activation == "capped_swiglu":
                 g, u = g.clamp(max=limit), u.clamp(min=-limit, max=limit)
                 y = g * torch.sigmoid(alpha * g) * (u + 1.0)
@@ -643,8 +667,9 @@ def moe_grouped(mode, a, weight, out, plan, top, activation="swiglu", limit=0.0,
     return out
 
 
-def moe_combine(y, out, top):
-    out.copy_(y.float().view(out.shape[0], top, -1).sum(1).to(out.dtype))
+def moe_combine(y, out, top, place=None):
+    rows = y if place is None else y[place.long()]
+    out.copy_(rows.float().view(out.shape[0], top, -1).sum(1).to(out.dtype))
     return out
 
 
@@ -652,7 +677,7 @@ def fused_decode_supports(*args) -> bool:
     return False      # the stand-ins rotate and store in `rope_kv_write`, never inside the attention
 
 
-ALL = ("moe_route", "moe_tile_rows", "moe_sort", "moe_grouped", "moe_combine", "sigmoid_gate_", "softcap_",
+ALL = ("moe_router", "moe_experts", "moe_route", "moe_tile_rows", "moe_sort", "moe_grouped", "moe_combine", "sigmoid_gate_", "softcap_",
        "head_norm_rope_kv_write", "sigmoid_gate_heads_", "mlstm", "embedding_streams", "stream_rmsnorm", "activation", "batched_linear", "latent_prep", "latent_attention",
        "gate_heads", "convert", "layernorm", "layernorm_add", "projection_rmsnorm_", "qk_projection_rmsnorm_", "gated_rmsnorm",
        "short_conv", "short_conv_step", "short_conv_update", "gated_delta_rule", "fused_decode_supports", "scatter_tokens", "embedding", "rmsnorm", "add_", "add_bias_", "act_mul", "act_mul_interleaved", "gated_linear_supported",
