@@ -120,10 +120,9 @@ moe_route_kernel(const float* __restrict__ logits, int tokens, int experts, int 
 
 // The router's product and the routing in one launch: logits[e] = sum_k x[k] * w[e][k] in 32-bit (lane l adds up
 // k = l, l + 32, ..., then the lanes' sums meet in a fixed tree: the same bits whatever else is in the step), then
-// `route_token`.  A block takes TOK tokens; its warps take the experts in turn.
-constexpr int kRouterWarps = 8;
-
-template <typename T, int TOK>
+// `route_token`.  A block takes TOK tokens; its warps take the experts in turn: eight warps for eight tokens of a wide
+// step, thirty-two for the one token of a narrow step, where a warp's chain of loads is what the launch waits for.
+template <typename T, int TOK, int kRouterWarps>
 __global__ void __launch_bounds__(kRouterWarps * 32)
 moe_router_kernel(const T* __restrict__ x, size_t x_stride, const float* __restrict__ w, int tokens, int K, int experts,
                   int top, int groups, int keep, int renormalise, int* __restrict__ ids, float* __restrict__ weights) {
@@ -139,7 +138,7 @@ moe_router_kernel(const T* __restrict__ x, size_t x_stride, const float* __restr
 #pragma unroll
     for (int t = 0; t < TOK; ++t) acc[t] = 0.f;
     if (wide) {
-#pragma unroll 4
+#pragma unroll 8
       for (int k = lane * 4; k < K; k += 128) {
         const float4 wv = *reinterpret_cast<const float4*>(we + k);
 #pragma unroll
@@ -512,13 +511,13 @@ LI_EXPORT int li_moe_router(int dtype, const void* x, size_t x_stride, const flo
   const bool wide = tokens > 128;
   const size_t smem = (size_t)(wide ? 8 : 1) * (experts + groups) * sizeof(float);
   if (smem > 48 * 1024) return LI_ERR_UNSUPPORTED;
-#define LI_ROUTER(T, TOK)                                                                                             \
-  return (int)launch_pdl(tokens, moe_router_kernel<T, TOK>, dim3((tokens + TOK - 1) / TOK), dim3(kRouterWarps * 32),   \
+#define LI_ROUTER(T, TOK, WARPS)                                                                                      \
+  return (int)launch_pdl(tokens, moe_router_kernel<T, TOK, WARPS>, dim3((tokens + TOK - 1) / TOK), dim3(WARPS * 32),   \
                          smem, stream, (const T*)x, x_stride, w, tokens, K, experts, top, groups, keep, renormalise,  \
                          ids, weights)
-  if (dtype == kFloat32) { if (wide) LI_ROUTER(float, 8); LI_ROUTER(float, 1); }
-  if (wide) LI_ROUTER(bf16, 8);
-  LI_ROUTER(bf16, 1);
+  if (dtype == kFloat32) { if (wide) LI_ROUTER(float, 8, 8); LI_ROUTER(float, 1, 32); }
+  if (wide) LI_ROUTER(bf16, 8, 8);
+  LI_ROUTER(bf16, 1, 32);
 #undef LI_ROUTER
 }
 

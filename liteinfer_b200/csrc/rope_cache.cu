@@ -25,7 +25,7 @@
 // blend and the rotation are 32-bit; each result is rounded once.
 //
 // `norm_flags`: bit 0, q and k are divided by their root mean square also where no weight is given; bit 1, the norm
-// (and its weight) comes behind the rotation instead of in front of it.
+// (and its weight) comes behind the rotation instead of in front of it.  `cs_scale` multiplies every cosine and sine.
 //
 // li_sigmoid_gate_heads multiplies head h of every row of x by sigmoid(gate[row, h]) in place; li_sigmoid_gate
 // every element by the sigmoid of its own gate.
@@ -44,7 +44,7 @@ head_norm_rope_kv_write_kernel(T* __restrict__ qkv, size_t row_stride, const int
                                int rotary_dim, int page_size, int num_pages, int v_dim,
                                const T* __restrict__ q_norm, const T* __restrict__ k_norm, float norm_eps,
                                const T* __restrict__ v_other, size_t v_other_stride,
-                               const float* __restrict__ lambda, int norm_flags) {
+                               const float* __restrict__ lambda, int norm_flags, float cs_scale) {
   extern __shared__ float shared[];  // cos[half], sin[half], then one head per warp
   const bool unit = norm_flags & 1, after = norm_flags & 2;
   const int t = blockIdx.x;
@@ -57,8 +57,8 @@ head_norm_rope_kv_write_kernel(T* __restrict__ qkv, size_t row_stride, const int
   float* head = shared + rotary_dim + warp * head_dim;
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
     const float angle = __fmul_rn((float)pos, inv_freq[i]);
-    cosv[i] = cosf(angle);
-    sinv[i] = sinf(angle);
+    cosv[i] = cosf(angle) * cs_scale;
+    sinv[i] = sinf(angle) * cs_scale;
   }
   const int seq = seq_of_token[t];
   const int page = seq < 0 ? -1 : block_table[(size_t)seq * table_stride + pos / page_size];
@@ -128,7 +128,7 @@ head_norm_rope_kv_write_vec_kernel(T* __restrict__ qkv, size_t row_stride, const
                                    int rotary_dim, int page_size, int num_pages, int v_dim,
                                    const T* __restrict__ q_norm, const T* __restrict__ k_norm, float norm_eps,
                                    const T* __restrict__ v_other, size_t v_other_stride,
-                                   const float* __restrict__ lambda, int group_shift, int norm_flags) {
+                                   const float* __restrict__ lambda, int group_shift, int norm_flags, float cs_scale) {
   constexpr int N = Vec16<T>::N;
   extern __shared__ float shared[];  // cos[half], sin[half]
   const bool unit = norm_flags & 1, after = norm_flags & 2;
@@ -141,8 +141,8 @@ head_norm_rope_kv_write_vec_kernel(T* __restrict__ qkv, size_t row_stride, const
   float* sinv = shared + half;
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
     const float angle = __fmul_rn((float)pos, inv_freq[i]);
-    cosv[i] = cosf(angle);
-    sinv[i] = sinf(angle);
+    cosv[i] = cosf(angle) * cs_scale;
+    sinv[i] = sinf(angle) * cs_scale;
   }
   const int seq = seq_of_token[t];
   const int page = seq < 0 ? -1 : block_table[(size_t)seq * table_stride + pos / page_size];
@@ -453,7 +453,7 @@ LI_EXPORT int li_head_norm_rope_kv_write(int dtype, void* qkv, size_t row_stride
                                          int kv_heads, int head_dim, int rotary_dim, int page_size, int num_pages,
                                          int v_dim, const void* q_norm, const void* k_norm, float norm_eps,
                                          const void* v_other, size_t v_other_stride, const float* lambda,
-                                         int norm_flags, cudaStream_t stream) {
+                                         int norm_flags, float cs_scale, cudaStream_t stream) {
   if (tokens == 0) return 0;
   if (v_dim < 1 || head_dim < 1) return LI_ERR_UNSUPPORTED;
   if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return LI_ERR_UNSUPPORTED;
@@ -478,12 +478,12 @@ LI_EXPORT int li_head_norm_rope_kv_write(int dtype, void* qkv, size_t row_stride
                                stream, (float*)qkv, row_stride, positions, seq_of_token, block_table, table_stride,
                                (float*)k_pool, (float*)v_pool, inv_freq, heads, kv_heads, head_dim, rotary_dim,
                                page_size, num_pages, v_dim, (const float*)q_norm, (const float*)k_norm, norm_eps,
-                               (const float*)v_other, v_other_stride, lambda, shift, norm_flags);
+                               (const float*)v_other, v_other_stride, lambda, shift, norm_flags, cs_scale);
       return (int)launch_pdl(tokens, head_norm_rope_kv_write_vec_kernel<bf16>, dim3(tokens), dim3(kPrepWarps * 32), cs,
                              stream, (bf16*)qkv, row_stride, positions, seq_of_token, block_table, table_stride,
                              (bf16*)k_pool, (bf16*)v_pool, inv_freq, heads, kv_heads, head_dim, rotary_dim, page_size,
                              num_pages, v_dim, (const bf16*)q_norm, (const bf16*)k_norm, norm_eps,
-                             (const bf16*)v_other, v_other_stride, lambda, shift, norm_flags);
+                             (const bf16*)v_other, v_other_stride, lambda, shift, norm_flags, cs_scale);
     }
   }
   const size_t smem = ((size_t)rotary_dim + (size_t)kPrepWarps * head_dim) * sizeof(float);
@@ -493,12 +493,12 @@ LI_EXPORT int li_head_norm_rope_kv_write(int dtype, void* qkv, size_t row_stride
                            stream, (float*)qkv, row_stride, positions, seq_of_token, block_table, table_stride,
                            (float*)k_pool, (float*)v_pool, inv_freq, heads, kv_heads, head_dim, rotary_dim, page_size,
                            num_pages, v_dim, (const float*)q_norm, (const float*)k_norm, norm_eps,
-                           (const float*)v_other, v_other_stride, lambda, norm_flags);
+                           (const float*)v_other, v_other_stride, lambda, norm_flags, cs_scale);
   return (int)launch_pdl(tokens, head_norm_rope_kv_write_kernel<bf16>, dim3(tokens), dim3(kPrepWarps * 32), smem, stream,
                          (bf16*)qkv, row_stride, positions, seq_of_token, block_table, table_stride, (bf16*)k_pool,
                          (bf16*)v_pool, inv_freq, heads, kv_heads, head_dim, rotary_dim, page_size, num_pages, v_dim,
                          (const bf16*)q_norm, (const bf16*)k_norm, norm_eps, (const bf16*)v_other, v_other_stride,
-                         lambda, norm_flags);
+                         lambda, norm_flags, cs_scale);
 }
 
 LI_EXPORT int li_sigmoid_gate_heads(int dtype, void* x, const void* gate, size_t gate_stride, int tokens, int heads,

@@ -50,7 +50,7 @@ _SIGNATURES = {
     "li_head_norm_rope_kv_write": ("rope_cache", [c_int, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p, c_int,
                                                   c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                                   c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p,
-                                                  c_size_t, c_void_p, c_int, c_void_p]),
+                                                  c_size_t, c_void_p, c_int, c_float, c_void_p]),
     "li_sigmoid_gate": ("rope_cache", [c_int, c_void_p, c_void_p, c_size_t, c_int, c_int, c_void_p]),
     "li_softcap": ("elementwise", [c_int, c_void_p, c_size_t, c_float, c_void_p]),
     "li_moe_route": ("moe", [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
@@ -702,7 +702,7 @@ def head_norm_rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, seq_of_t
                             q_norm: torch.Tensor | None, k_norm: torch.Tensor | None, norm_eps: float,
                             store: bool = True, v_other: torch.Tensor | None = None,
                             blend: torch.Tensor | None = None, unit_norm: bool = False,
-                            norm_after_rotation: bool = False) -> None:
+                            norm_after_rotation: bool = False, cos_sin_scale: float = 1.0) -> None:
     """`rope_kv_write` for an attention whose q and k pass a root-mean-square norm per head first: every q head
     becomes rot(q_norm * q / sqrt(mean(q^2) + eps)) in place, every k head likewise (with k_norm) on its way into
     its page; None leaves that projection unnormalised.  q_norm and k_norm: [head_dim], the dtype of qkv.
@@ -712,7 +712,8 @@ def head_norm_rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, seq_of_t
     (a column slice is fine) with `blend` (one float32 on the device): what is stored is
     (1 - blend) * v + blend * v_other, computed in 32-bit and rounded once.  `unit_norm`: q and k are divided by
     their root mean square per head also where no weight is given.  `norm_after_rotation`: the norm (of the rotated
-    head, with its weight if any) comes behind the rotation instead of in front of it."""
+    head, with its weight if any) comes behind the rotation instead of in front of it.  `cos_sin_scale` multiplies
+    every cosine and sine."""
     _rows2d(qkv, "qkv")
     _on_gpu(positions, seq_of_token, block_table, k_pool, v_pool, inv_freq, q_norm, k_norm, blend)
     _int32(positions, "positions"); _int32(seq_of_token, "seq_of_token"); _int32(block_table, "block_table")
@@ -735,7 +736,8 @@ def head_norm_rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, seq_of_t
         block_table.data_ptr(), block_table.stride(0), k_pool.data_ptr(), v_pool.data_ptr(), _ptr(inv_freq), tokens,
         heads, kv_heads, head_dim, rotary_dim if inv_freq is not None else 0, page_size, pages if store else 0, vd,
         _ptr(q_norm), _ptr(k_norm), float(norm_eps), _ptr(v_other), v_other.stride(0) if v_other is not None else 0,
-        _ptr(blend), int(unit_norm) | (2 if norm_after_rotation else 0), _stream()), "head_norm_rope_kv_write")
+        _ptr(blend), int(unit_norm) | (2 if norm_after_rotation else 0), float(cos_sin_scale), _stream()),
+        "head_norm_rope_kv_write")
 
 
 def sigmoid_gate_(x: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:

@@ -219,8 +219,6 @@ class Attention:
         if rotary is None:
             self.position.apply(qkv[:, :q_width].unflatten(1, (self.heads, self.head_dim)),
                                 qkv[:, q_width:q_width + kv_width].unflatten(1, (self.kv_heads, self.head_dim)), ctx)
-        elif rotary.attention_scaling != 1.0:
-            raise ValueError("this attention path rotates with plain cosines and sines (no stretch)")
         values = qkv[:, q_width + kv_width:q_width + kv_width + v_width]
         other = None
         if self.value_mix == "source":
@@ -234,6 +232,8 @@ class Attention:
         options = {}
         if per_head and (not self.qk_norm_weight or self.qk_norm_after_rotation):
             options = dict(unit_norm=not self.qk_norm_weight, norm_after_rotation=self.qk_norm_after_rotation)
+        if rotary is not None and rotary.attention_scaling != 1.0:
+            options["cos_sin_scale"] = rotary.attention_scaling
         ops.head_norm_rope_kv_write(qkv, ctx.positions, ctx.seq_of_token, table, kv.k_pool, kv.v_pool,
                                     rotary.inv_freq if rotary else None, self.heads, self.kv_heads, self.head_dim,
                                     rotary.rotary_dim if rotary else 0,

@@ -7,9 +7,10 @@ KUT_B: what a configuration may leave out: no windows in two layers, no embeddin
 soft-cap, experts without groups with the best one of three chosen; a window of one token (a position sees itself
 only); one head; every dimension rotated; a latent layer whose frequencies are not scaled.
 KUT_C: sizes of the tensor-core kernels (keys and values of 64 with windows longer than a tile of keys, a latent of
-64 with a rotated part of 32, experts whose products run on mma.sync tiles).
+64 with a rotated part of 32, experts whose products run on tensor-core tiles).
 KUT_D: small sizes that are multiples of little (width 36, heads of 6 with 2 dimensions rotated, values of 10, a
-latent of 20 with a rotated part of 4, eight experts in four groups of which one is kept, experts 10 wide).
+latent of 20 with a rotated part of 4, eight experts in four groups of which one is kept, experts 10 wide; an
+attention layer whose frequencies are scaled too).
 KUT_E: a width of 512 with heads of 128 x 128 and windows of some hundred tokens, a latent of 128 with a rotated
 part of 64: prompts of a few hundred tokens take the tensor-core products and attention kernels.
 """
@@ -99,7 +100,8 @@ KUT_D = {
                  "router": {"experts": 8, "top": 2, "groups": {"count": 4, "keep": 1}}}},
         {"type": "attention",
          "mixer": {"heads": 4, "kv_heads": 2, "dim": 12, "vdim": 4, "scale": 0.2, "mask": {"size": 21},
-                   "rot": {"dims": 12, "base": 900.0}},
+                   "rot": {"dims": 8, "base": 900.0,
+                           "scaling": {"factor": 2.5, "original": 16, "fast": 8.0, "slow": 1.0}}},
          "mlp": {"kind": "dense", "ff": 28}},
         {"type": "latent_attention",
          "mixer": {"heads": 5, "dim": 6, "rot_dim": 4, "vdim": 5, "kv_rank": 20, "scale": 0.33, "mask": {"size": 8},

@@ -69,6 +69,8 @@ def test_unit_norm_behind_the_rotation(dtype, heads, kv_heads, head_dim, v_dim, 
     kn = (1 + 0.2 * _randn(head_dim, seed=3)).to(dtype) if weights else None
     pools = [[torch.zeros(12, kv_heads, page, n, dtype=dtype, device=DEV) for n in (head_dim, v_dim)] for _ in range(2)]
     options = dict(unit_norm=not weights, norm_after_rotation=after)
+    if weights and rot:
+        options["cos_sin_scale"] = 1.3          # stretched cosines and sines: the rotation then changes a head's norm
     for impl, qkv, (kp, vp) in ((ops, rows[0], pools[0]), (ref, rows[1], pools[1])):
         impl.head_norm_rope_kv_write(qkv, positions, seq_of, table, kp, vp, inv_freq, heads, kv_heads, head_dim, rot,
                                      qn, kn, 1e-5, **options)

@@ -282,7 +282,7 @@ def gated_rmsnorm(x, gate, weight, eps, out, heads, gate_activation="silu", den=
 
 def head_norm_rope_kv_write(qkv, positions, seq_of_token, block_table, k_pool, v_pool, inv_freq, heads, kv_heads,
                             head_dim, rotary_dim, q_norm, k_norm, norm_eps, store=True, v_other=None, blend=None,
-                            unit_norm=False, norm_after_rotation=False):
+                            unit_norm=False, norm_after_rotation=False, cos_sin_scale=1.0):
     """Per-head norms of q and k, the blend of v, then what `rope_kv_write` does, on a compact copy of the row.
     With the norm behind the rotation, q and k are rotated here and stored unrotated-as-they-are."""
     T, dtype = qkv.shape[0], qkv.dtype
@@ -292,8 +292,8 @@ def head_norm_rope_kv_write(qkv, positions, seq_of_token, block_table, k_pool, v
     k = qkv[:, qw:qw + kw].float().view(T, kv_heads, head_dim)
     v = qkv[:, qw + kw:qw + kw + vw].float()
     if norm_after_rotation and inv_freq is not None and rotary_dim > 0:
-        q, k = _turn(q, positions, inv_freq, rotary_dim), _turn(k, positions, inv_freq, rotary_dim)
-        inv_freq, rotary_dim = None, 0
+        q, k = _turn(q, positions, inv_freq, rotary_dim, cos_sin_scale), _turn(k, positions, inv_freq, rotary_dim, cos_sin_scale)
+        inv_freq, rotary_dim, cos_sin_scale = None, 0, 1.0
     if q_norm is not None or unit_norm:
         q = _norm(q, norm_eps, centre=False) * (q_norm.float() if q_norm is not None else 1.0)
     if k_norm is not None or unit_norm:
@@ -307,7 +307,7 @@ def head_norm_rope_kv_write(qkv, positions, seq_of_token, block_table, k_pool, v
     if dtype != torch.float32:
         wide_k.copy_(k_pool); wide_v.copy_(v_pool)
     rope_kv_write(compact, positions, seq_of_token, block_table, wide_k, wide_v, inv_freq, heads, kv_heads, head_dim,
-                  rotary_dim, store=store, v_head_dim=vd)
+                  rotary_dim, store=store, v_head_dim=vd, cos_sin_scale=cos_sin_scale)
     if dtype != torch.float32:
         k_pool.copy_(wide_k); v_pool.copy_(wide_v)
     qkv[:, :qw] = compact[:, :qw].to(dtype)
