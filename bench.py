@@ -354,16 +354,16 @@ def _kutolix_config(width: int, ff: int, layers: int, heads: int, kv_heads: int,
     h = heads * head_dim // 128
     attention = {"type": "attention", "mlp": {"kind": "dense", "ff": ff},
                  "mixer": {"heads": h, "kv_heads": max(1, h // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
-                           "mask": {"size": 1024}, "rot": {"dims": 64, "base": 250000.0}}}
+                           "mask": {"size": 1024}, "rot": {"dims": 64, "base": 100000.0}}}
     latent = {"type": "latent_attention",
               "mlp": {"kind": "moe", "expert": {"ff": ff // 4, "limit": 7.0},
                       "router": {"experts": 32, "top": 4, "groups": {"count": 8, "keep": 4}}},
               "mixer": {"heads": h, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "scale": 192 ** -0.5,
                         "mask": {"size": 1024},
                         "rot": {"dims": 64, "base": 10000.0,
-                                "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}}
-    return {"architecture": "Kutolix", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 0.5},
-            "residual_mult": 0.5, "logit_softcap": 15.0, "layers": [(attention, latent)[i % 2] for i in range(layers)]}
+                                "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    return {"architecture": "Kutolix", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 2.0},
+            "residual_mult": 0.7, "logit_softcap": 30.0, "layers": [(attention, latent)[i % 2] for i in range(layers)]}
 
 
 def _timed(fn, repeats: int = 20, warmup: int = 5, inner: int = 1) -> float:
@@ -774,7 +774,7 @@ def _kutolix_kernels(peaks: dict) -> dict:
     kp, vp = (torch.empty(pages_t, kvh, page, hd, dtype=bf, device=dev) for _ in range(2))
     table = torch.arange(pages_t, dtype=torch.int32, device=dev).view(1, pages_t)
     positions, seq_of = torch.arange(T, dtype=torch.int32, device=dev), torch.zeros(T, dtype=torch.int32, device=dev)
-    inv_half = (250000.0 ** (-torch.arange(0, hd // 2, 2, dtype=torch.float32) / (hd // 2))).to(dev)
+    inv_half = (100000.0 ** (-torch.arange(0, hd // 2, 2, dtype=torch.float32) / (hd // 2))).to(dev)
     norm_w = torch.ones(hd, dtype=bf, device=dev)
     moved = T * hd * 2 * (2 * heads + 4 * kvh)
     ms = _timed(lambda: ops.head_norm_rope_kv_write(qkv, positions, seq_of, table, kp, vp, inv_half, heads, kvh, hd, hd // 2,
@@ -844,7 +844,7 @@ def _kutolix_kernels(peaks: dict) -> dict:
 
     # -- the soft cap on 64 rows of logits
     logits = torch.randn(64, 32000, device=dev).to(bf)
-    out["softcap_b64_us"] = in_graph(lambda: ops.softcap_(logits, 15.0)) * 1e3
+    out["softcap_b64_us"] = in_graph(lambda: ops.softcap_(logits, 30.0)) * 1e3
     return {k: round(v, 4) for k, v in out.items()}
 
 

@@ -124,7 +124,7 @@ KUT_E = {
         {"type": "latent_attention",
          "mixer": {"heads": 4, "dim": 64, "rot_dim": 64, "vdim": 64, "kv_rank": 128, "scale": 0.09, "mask": {"size": 180},
                    "rot": {"dims": 64, "base": 10000.0,
-                           "scaling": {"factor": 4.0, "original": 128, "fast": 32.0, "slow": 1.0}}},
+                           "scaling": {"factor": 6.0, "original": 128, "fast": 24.0, "slow": 1.0}}},
          "mlp": {"kind": "dense", "ff": 768}},
         {"type": "attention",
          "mixer": {"heads": 4, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 0.1, "mask": {"size": 333},

@@ -98,7 +98,7 @@ def _sink_case(dtype, heads, kv_heads, d, page, q_lens, ctx_lens):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads,kv_heads,d,page,window", [(4, 2, 16, 16, 0), (6, 3, 48, 8, 7), (3, 1, 32, 4, 40), (2, 2, 80, 16, 1)])
+@pytest.mark.parametrize("heads,kv_heads,d,page,window", [(4, 2, 16, 16, 0), (6, 3, 48, 8, 7), (3, 1, 32, 4, 37), (2, 2, 80, 16, 1)])
 def test_sink_on_the_plain_kernel(dtype, heads, kv_heads, d, page, window):
     from liteinfer_b200 import ops
 
@@ -179,7 +179,7 @@ def test_one_key_stands_out_against_a_sink_at_the_windows_edge(d, page, decode):
 
 # ------------------------------------------------------------------ latent attention: window and stretch
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads,c,r,dims,d,page,window", [(3, 40, 10, 6, 12, 4, 13), (1, 24, 2, 2, 5, 8, 1), (6, 96, 32, 32, 16, 16, 40),
+@pytest.mark.parametrize("heads,c,r,dims,d,page,window", [(3, 40, 10, 6, 12, 4, 13), (1, 24, 2, 2, 5, 8, 1), (6, 96, 32, 32, 16, 16, 50),
                                                           (16, 64, 32, 32, 32, 16, 45), (9, 128, 64, 64, 8, 64, 100)])
 def test_latent_attention_with_a_window_and_stretched_rotation(dtype, heads, c, r, dims, d, page, window):
     from liteinfer_b200 import ops
@@ -282,7 +282,7 @@ def test_latent_prep_without_a_query_latent_and_with_stretch(dtype):
 
 
 # ------------------------------------------------------------------ the mixture of experts
-@pytest.mark.parametrize("experts,top,groups,keep", [(6, 2, 3, 2), (12, 3, 3, 2), (8, 2, 4, 1), (64, 6, 8, 3), (5, 2, 1, 1),
+@pytest.mark.parametrize("experts,top,groups,keep", [(6, 2, 3, 2), (12, 4, 4, 2), (8, 2, 4, 1), (64, 6, 8, 3), (5, 2, 1, 1),
                                                       (3, 1, 1, 1), (256, 8, 8, 4), (4, 4, 2, 2)])
 @pytest.mark.parametrize("renormalise", [False, True])
 def test_router_against_the_plain_mechanism(experts, top, groups, keep, renormalise):
