@@ -74,13 +74,14 @@ struct TcAttnParams {
   int heads, kv_heads, page_size, page_shift, num_pages;
   float scale_log2;
   int window;
-  int* error_flag;
   // With a window, the first keep_first keys of a sequence stay visible behind it.  cap_out > 0: an unscaled score
   // s becomes cap_out * tanh(s * cap_in) and is then scaled like any other (cap_in = scale / cap, cap_out = cap / scale).
   int keep_first;
+  int* error_flag;
   float cap_in, cap_out;
   const float* sink;      // [heads] float or null: exp(sink[h]) is one more term of head h's denominator (no key, no value)
 };
+static_assert(sizeof(TcAttnParams) == 128, "the fields are ordered so that the parameters stay 128 bytes");
 
 // tanh(x) = 1 - 2 / (1 + e^(2x)) from one exponential and one division; exact at both ends, a few 1e-7 between.
 __device__ __forceinline__ float tanh_fast(float x) {
@@ -454,7 +455,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
       tcgen05_fence_after();
       const int qi = q0 + row / groups, head = kvh * groups + row % groups;
       // The exponentials were taken against m (unscaled), so the sink's term is too.
-      if (p.sink != nullptr && row < rows_used) l += exp2f(p.sink[head] * kLog2eF - m * p.scale_log2);
+      // (Compiled into the kernel's form with options only, so that the plain form is what it was.)
+      if (kOptions && p.sink != nullptr && row < rows_used) l += exp2f(p.sink[head] * kLog2eF - m * p.scale_log2);
       const float inv = l > 0.f ? 1.f / l : 0.f;
       bf16* dst = p.out + (size_t)(q_begin + qi) * p.out_row_stride + (size_t)head * D;
 #pragma unroll
@@ -522,7 +524,7 @@ static int launch_tc_attention_as(const CUtensorMap& mk, const CUtensorMap& mv, 
 template <int D, int X>
 static int launch_tc_attention(const CUtensorMap& mk, const CUtensorMap& mv, const TcAttnParams& p, dim3 grid,
                                cudaStream_t stream) {
-  return (p.keep_first > 0 || p.cap_out > 0.f) ? launch_tc_attention_as<D, X, true>(mk, mv, p, grid, stream)
+  return (p.keep_first > 0 || p.cap_out > 0.f || p.sink != nullptr) ? launch_tc_attention_as<D, X, true>(mk, mv, p, grid, stream)
                                                 : launch_tc_attention_as<D, X, false>(mk, mv, p, grid, stream);
 }
 
@@ -578,7 +580,7 @@ LI_EXPORT int li_paged_attention_tcgen05(const void* q, int q_row_stride, void* 
   while ((1 << shift) < page_size) ++shift;
   TcAttnParams p{(const bf16*)q, q_row_stride, (bf16*)out, out_row_stride, block_table, table_stride,
                  query_start_loc, context_lens, seq_index, heads, kv_heads, page_size, shift, num_pages,
-                 scale * kLog2eF, window, error_flag, window > 0 && keep_first > 0 ? keep_first : 0,
+                 scale * kLog2eF, window, window > 0 && keep_first > 0 ? keep_first : 0, error_flag,
                  softcap > 0.f ? scale / softcap : 0.f, softcap > 0.f ? softcap / scale : 0.f, sink};
   const int groups = heads / kv_heads;
   const int tq = kRows / groups;

@@ -31,12 +31,17 @@ constexpr int kTileK = 64;                 // 64 bf16 = 128 bytes = one swizzle 
 constexpr int kUmmaK = 16;
 constexpr int kGemmThreads = 192;          // loader, issuer, four epilogue warps
 constexpr int kPairThreads = 320;          // the kernel for pairs of CTAs: loader, issuer, eight epilogue warps
-__device__ __forceinline__ float gated_value(float gate, float up, int act, float limit = 0.f, float alpha = 1.f) {
-  if (act == 4) {     // an expert's capped form, all of it in 32-bit: min(g, L) * sigmoid(alpha * min(g, L)) * (clamp(u, -L, L) + 1)
+__device__ __forceinline__ float gated_value(float gate, float up, int act);
+// With an expert's capped form (act 4), all of it in 32-bit: min(g, L) * sigmoid(alpha * min(g, L)) * (clamp(u, -L, L) + 1).
+__device__ __forceinline__ float gated_value(float gate, float up, int act, float limit, float alpha) {
+  if (act == 4) {
     gate = fminf(gate, limit);
     up = fminf(fmaxf(up, -limit), limit);
     return gate * (1.0f / (1.0f + expf(-alpha * gate))) * (up + 1.0f);
   }
+  return gated_value(gate, up, act);
+}
+__device__ __forceinline__ float gated_value(float gate, float up, int act) {
   gate = __bfloat162float(__float2bfloat16_rn(gate));
   up = __bfloat162float(__float2bfloat16_rn(up));
   float a;
@@ -66,10 +71,14 @@ struct GemmParams {
   int M, N, K;
   int gated_act;
   int* error_flag;
-  // A product grouped by expert (tile_expert != null; the single-CTA kernel only): x holds the rows of all experts,
-  // expert by expert (rows [offsets[e], offsets[e + 1]) are expert e's), w the experts' matrices one below the other
-  // (N rows each), and row tile t of the launch is 128 rows of expert tile_expert[t] (-1: no such tile) from row
-  // tile_row0[t] on.  Rows of a tile behind its expert's last are computed and not stored.
+};
+
+// A product grouped by expert (tile_expert != null; the single-CTA kernel only, as a parameter of its own so that the
+// plain product's parameters are what they were): x holds the rows of all experts, expert by expert (rows
+// [offsets[e], offsets[e + 1]) are expert e's), w the experts' matrices one below the other (N rows each), and row
+// tile t of the launch is 128 rows of expert tile_expert[t] (-1: no such tile) from row tile_row0[t] on.  Rows of a
+// tile behind its expert's last are computed and not stored.
+struct GroupParams {
   const int* tile_expert;
   const int* tile_row0;
   const int* offsets;
@@ -83,10 +92,14 @@ struct GemmParams {
 // 32 consecutive columns of one output row, from the accumulator's registers to global memory: rounded to
 // bfloat16 (with the bias), or for a gated feed-forward two groups of (eight gate, eight up) columns turned into
 // 16 outputs.  The caller has checked m < M and n0 < N.
-__device__ __forceinline__ void store_chunk(const GemmParams& p, const unsigned (&r)[32], int m, int n0) {
+// `kGrouped`: the ways out that only a product grouped by expert has (a row's scale, the experts' capped activation)
+// are compiled into that form alone, so the plain product's epilogue is what it was.
+template <bool kGrouped>
+__device__ __forceinline__ void store_chunk(const GemmParams& p, const GroupParams& g, const unsigned (&r)[32], int m,
+                                            int n0) {
   if (p.gated_act < 0) {
     bf16* dst = p.out + (size_t)m * p.N + n0;
-    const float scale = p.row_scale != nullptr ? p.row_scale[p.row_of[m]] : 1.0f;
+    const float scale = (kGrouped && g.row_scale != nullptr) ? g.row_scale[g.row_of[m]] : 1.0f;
     if (n0 + 32 <= p.N && (p.N % 8) == 0) {
 #pragma unroll
       for (int v = 0; v < 4; ++v) {
@@ -94,7 +107,8 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, const unsigned 
         unsigned* w = reinterpret_cast<unsigned*>(&pack);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          float lo = __uint_as_float(r[v * 8 + 2 * j]) * scale, hi = __uint_as_float(r[v * 8 + 2 * j + 1]) * scale;
+          float lo = __uint_as_float(r[v * 8 + 2 * j]), hi = __uint_as_float(r[v * 8 + 2 * j + 1]);
+          if (kGrouped) { lo *= scale; hi *= scale; }
           if (p.bias) {
             lo += __bfloat162float(p.bias[n0 + v * 8 + 2 * j]);
             hi += __bfloat162float(p.bias[n0 + v * 8 + 2 * j + 1]);
@@ -108,7 +122,8 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, const unsigned 
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
         if (n0 + j < p.N) {
-          float v = __uint_as_float(r[j]) * scale;
+          float v = __uint_as_float(r[j]);
+          if (kGrouped) v *= scale;
           if (p.bias) v += __bfloat162float(p.bias[n0 + j]);
           dst[j] = __float2bfloat16_rn(v);
         }
@@ -134,7 +149,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, const unsigned 
             gate += __bfloat162float(p.bias[n0 + col]);
             up += __bfloat162float(p.bias[n0 + col + 8]);
           }
-          v[e] = gated_value(gate, up, p.gated_act, p.limit, p.alpha);
+          v[e] = kGrouped ? gated_value(gate, up, p.gated_act, g.limit, g.alpha) : gated_value(gate, up, p.gated_act);
         }
         __nv_bfloat162 h = __floats2bfloat162_rn(v[0], v[1]);
         w[j] = *reinterpret_cast<unsigned*>(&h);
@@ -147,7 +162,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, const unsigned 
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                    const GemmParams p) {
+                    const GemmParams p, const GroupParams g) {
   extern __shared__ unsigned char smem_raw[];
   // Tiles must start on 1024-byte boundaries for the 128-byte swizzle.
   const unsigned base = (smem_addr(smem_raw) + 1023u) & ~1023u;
@@ -161,8 +176,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   __shared__ unsigned tmem_base_shared;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const bool grouped = p.tile_expert != nullptr;
-  const int tiles_m = grouped ? p.row_tiles : (p.M + kTileM - 1) / kTileM, tiles_n = (p.N + BN - 1) / BN;
+  const bool grouped = g.tile_expert != nullptr;
+  const int tiles_m = grouped ? g.row_tiles : (p.M + kTileM - 1) / kTileM, tiles_n = (p.N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
   const int k_blocks = (p.K + kTileK - 1) / kTileK;
 
@@ -204,9 +219,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         tile_coords(tile, tiles_m, tiles_n, tm, tn);
         // A grouped product: the tile's rows start where its expert's run says, its weights where the expert's lie.
         // All three roles skip a tile that the table does not have, each by its own look.
-        const int expert = grouped ? p.tile_expert[tm] : 0;
+        const int expert = grouped ? g.tile_expert[tm] : 0;
         if (expert < 0) continue;
-        const int row0 = grouped ? p.tile_row0[tm] : tm * kTileM;
+        const int row0 = grouped ? g.tile_row0[tm] : tm * kTileM;
         const int w_row0 = expert * p.N + tn * BN;
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1, p.error_flag, 1)) { ok = false; break; }
@@ -232,7 +247,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         if (grouped) {
           int tm, tn;
           tile_coords(tile, tiles_m, tiles_n, tm, tn);
-          if (p.tile_expert[tm] < 0) continue;
+          if (g.tile_expert[tm] < 0) continue;
         }
         const int buf = local & 1;
         const unsigned use = (unsigned)(local >> 1);
@@ -261,15 +276,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
       int tm, tn;
       tile_coords(tile, tiles_m, tiles_n, tm, tn);
-      const int expert = grouped ? p.tile_expert[tm] : 0;
+      const int expert = grouped ? g.tile_expert[tm] : 0;
       if (expert < 0) continue;
-      const int m_end = grouped ? p.offsets[expert + 1] : p.M;
+      const int m_end = grouped ? g.offsets[expert + 1] : p.M;
       const int buf = local & 1;
       const unsigned use = (unsigned)(local >> 1);
       ++local;
       if (!mbar_wait(acc_full_bar(buf), use & 1, p.error_flag, 4)) { ok = false; break; }
       tcgen05_fence_after();
-      const int m = (grouped ? p.tile_row0[tm] : tm * kTileM) + quarter * 32 + lane;
+      const int m = (grouped ? g.tile_row0[tm] : tm * kTileM) + quarter * 32 + lane;
       const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(buf * BN);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -279,7 +294,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         tmem_load_wait();
         const int n0 = tn * BN + c * 32;
         if (m >= m_end || n0 >= p.N) continue;
-        store_chunk(p, r, m, n0);
+        if (grouped) store_chunk<true>(p, g, r, m, n0);
+        else store_chunk<false>(p, g, r, m, n0);
       }
       tcgen05_fence_before();
       __syncwarp();
@@ -424,7 +440,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         tmem_load_wait();
         const int n0 = tn * BN + c * 32;
         if (m >= p.M || n0 >= p.N) continue;
-        store_chunk(p, r, m, n0);
+        store_chunk<false>(p, GroupParams{}, r, m, n0);
       }
       tcgen05_fence_before();
       __syncwarp();
@@ -470,7 +486,8 @@ static bool make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box
 }
 
 template <int BN, int STAGES>
-static int launch_gemm(const CUtensorMap& mx, const CUtensorMap& mw, const GemmParams& p, int sms, cudaStream_t s) {
+static int launch_gemm(const CUtensorMap& mx, const CUtensorMap& mw, const GemmParams& p, int sms, cudaStream_t s,
+                       const GroupParams& g = GroupParams{}) {
   constexpr size_t smem = (size_t)STAGES * (kTileM + BN) * kTileK * 2 + 8 * (2 * STAGES + 4) + 16 + 1024;
   static bool configured = false;
   if (!configured) {
@@ -479,9 +496,9 @@ static int launch_gemm(const CUtensorMap& mx, const CUtensorMap& mw, const GemmP
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  const int tiles = (p.tile_expert != nullptr ? p.row_tiles : (p.M + kTileM - 1) / kTileM) * ((p.N + BN - 1) / BN);
+  const int tiles = (g.tile_expert != nullptr ? g.row_tiles : (p.M + kTileM - 1) / kTileM) * ((p.N + BN - 1) / BN);
   const int grid = tiles < sms ? tiles : sms;
-  gemm_tcgen05_kernel<BN, STAGES><<<grid, kGemmThreads, smem, s>>>(mx, mw, p);
+  gemm_tcgen05_kernel<BN, STAGES><<<grid, kGemmThreads, smem, s>>>(mx, mw, p, g);
   return (int)cudaGetLastError();
 }
 
@@ -581,10 +598,12 @@ LI_EXPORT int li_gemm_tcgen05_grouped(const void* x, const void* w, void* out, i
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
     if (sms <= 0) sms = 148;
   }
-  const bool wide = N >= 256;
+  // LITEINFER_GROUPED_TILE_N=128 keeps the narrow tile (six stages of 32 KB instead of four of 48) at every width.
+  static const bool narrow = [] { const char* e = getenv("LITEINFER_GROUPED_TILE_N"); return e && atoi(e) == 128; }();
+  const bool wide = N >= 256 && !narrow;
   CUtensorMap mx, mw;
   if (!make_map(&mx, x, rows, K, kTileM) || !make_map(&mw, w, experts * N, K, wide ? 256 : 128)) return LI_ERR_UNSUPPORTED;
-  GemmParams p{(bf16*)out, nullptr, rows, N, K, gated_act, error_flag, tile_expert, tile_row0, offsets, row_tiles,
-               row_of, row_scale, limit, alpha};
-  return wide ? launch_gemm<256, 4>(mx, mw, p, sms, stream) : launch_gemm<128, 6>(mx, mw, p, sms, stream);
+  GemmParams p{(bf16*)out, nullptr, rows, N, K, gated_act, error_flag};
+  GroupParams g{tile_expert, tile_row0, offsets, row_tiles, row_of, row_scale, limit, alpha};
+  return wide ? launch_gemm<256, 4>(mx, mw, p, sms, stream, g) : launch_gemm<128, 6>(mx, mw, p, sms, stream, g);
 }
