@@ -598,7 +598,8 @@ LI_EXPORT int li_gemm_tcgen05_grouped(const void* x, const void* w, void* out, i
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
     if (sms <= 0) sms = 148;
   }
-  // LITEINFER_GROUPED_TILE_N=128 keeps the narrow tile (six stages of 32 KB instead of four of 48) at every width.
+  // LITEINFER_GROUPED_TILE_N=128 keeps the narrow tile (six stages of 32 KB instead of four of 48) at every width
+  // (measured at 32 experts of 2,048 x 2,048, four a token: 406 against 348 us for 2,048 tokens, 1,118 against 903 for 8,192).
   static const bool narrow = [] { const char* e = getenv("LITEINFER_GROUPED_TILE_N"); return e && atoi(e) == 128; }();
   const bool wide = N >= 256 && !narrow;
   CUtensorMap mx, mw;

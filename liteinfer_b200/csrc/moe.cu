@@ -426,19 +426,37 @@ moe_grouped_mma_kernel(const bf16* __restrict__ a, size_t a_stride, const bf16* 
 }
 
 // ---------------------------------------------------------------------------------------- combine
-template <typename T>
+// `kVec`: 16 bytes of a row a thread (width a multiple of the vector's length); the sums are the same either way.
+template <typename T, bool kVec>
 __global__ void moe_combine_kernel(const T* __restrict__ y, T* __restrict__ out, size_t tokens, int top, int width,
                                    const int* __restrict__ place) {
+  constexpr int N = kVec ? Vec16<T>::N : 1;
   grid_dependency_wait();
-  const size_t total = tokens * width;
+  const size_t per_row = (size_t)width / N, total = tokens * per_row;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-    const size_t t = i / width, c = i - t * width;
-    float sum = 0.f;
+    const size_t t = i / per_row, c = (i - t * per_row) * N;
+    float sum[N];
+#pragma unroll
+    for (int e = 0; e < N; ++e) sum[e] = 0.f;
     for (int s = 0; s < top; ++s) {
       const size_t row = place != nullptr ? (size_t)place[t * top + s] : t * top + s;
-      sum += to_float(y[row * width + c]);
+      if (kVec) {
+        float v[Vec16<T>::N];
+        unpack16(load16(y + row * width + c), v);
+#pragma unroll
+        for (int e = 0; e < N; ++e) sum[e] += v[e];
+      } else {
+        sum[0] += to_float(y[row * width + c]);
+      }
     }
-    out[i] = from_float<T>(sum);
+    if (kVec) {
+      Vec16<T> o;
+#pragma unroll
+      for (int e = 0; e < N; ++e) o.set(e, sum[e]);
+      store16(out + t * width + c, o);
+    } else {
+      out[t * width + c] = from_float<T>(sum[0]);
+    }
   }
 }
 
@@ -568,12 +586,16 @@ LI_EXPORT int li_moe_grouped(int dtype, int mode, const void* a, size_t a_stride
 // itself, or place[pair] where `place` is given (rows in the order of the experts' runs).
 LI_EXPORT int li_moe_combine(int dtype, const void* y, void* out, int tokens, int top, int width, const int* place,
                              cudaStream_t stream) {
-  const size_t total = (size_t)tokens * width;
-  if (total == 0) return 0;
+  if ((size_t)tokens * width == 0) return 0;
+  const int n = dtype == kFloat32 ? 4 : 8;
+  const bool vec = width % n == 0 && aligned16(y) && aligned16(out);
+  const size_t total = (size_t)tokens * width / (vec ? n : 1);
   const dim3 grid((unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16));
-  if (dtype == kFloat32)
-    return (int)launch_pdl(tokens, moe_combine_kernel<float>, grid, dim3(256), 0, stream, (const float*)y, (float*)out,
-                           (size_t)tokens, top, width, place);
-  return (int)launch_pdl(tokens, moe_combine_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16*)y, (bf16*)out,
-                         (size_t)tokens, top, width, place);
+#define LI_COMBINE(T, V)                                                                                             \
+  return (int)launch_pdl(tokens, moe_combine_kernel<T, V>, grid, dim3(256), 0, stream, (const T*)y, (T*)out,          \
+                         (size_t)tokens, top, width, place)
+  if (dtype == kFloat32) { if (vec) LI_COMBINE(float, true); LI_COMBINE(float, false); }
+  if (vec) LI_COMBINE(bf16, true);
+  LI_COMBINE(bf16, false);
+#undef LI_COMBINE
 }
