@@ -138,6 +138,57 @@ ALL = {"kut_a": (KUT_A, 41, 16), "kut_b": (KUT_B, 42, 4), "kut_c": (KUT_C, 43, 1
        "kut_e": (KUT_E, 45, 16)}
 
 
+def random_config(seed: int) -> dict:
+    """A configuration drawn at random: three to six layers of either mixer with sizes of the SIMT kernels and of the
+    tensor-core ones, windows or none, rotations or none, every kind of feed-forward or none."""
+    rng = random.Random(seed)
+    layers = []
+    for _ in range(rng.randint(3, 6)):
+        window = rng.choice([None, 17, 24, 50, 64, 100, 130])
+        if rng.random() < 0.5:
+            dim = rng.choice([32, 48, 64, 128])
+            heads = rng.choice([2, 4, 6, 8])
+            mixer = {"heads": heads, "kv_heads": rng.choice([k for k in (1, 2, 3, 4, 8) if heads % k == 0]), "dim": dim,
+                     "vdim": rng.choice([dim, dim, 32, 64, 128]), "scale": dim ** -0.5}
+            if rng.random() < 0.8:
+                mixer["rot"] = {"dims": rng.choice([d for d in (8, 16, 32, 64, 128) if d <= dim]),
+                                "base": rng.choice([10000.0, 100000.0, 500.0])}
+            kind = "attention"
+        else:
+            kv_rank, rot_dim = rng.choice([(64, 32), (128, 32), (128, 64), (128, 8), (96, 16), (256, 64), (48, 8)])
+            scaling = rng.choice([None, {"factor": rng.choice([2.0, 3.0, 8.0]), "original": rng.choice([64, 256, 2048]),
+                                         "fast": rng.choice([16.0, 32.0]), "slow": 1.0}])
+            mixer = {"heads": rng.choice([2, 4, 8]), "dim": rng.choice([16, 32, 64]), "rot_dim": rot_dim,
+                     "vdim": rng.choice([24, 32, 48, 64]), "kv_rank": kv_rank, "scale": 0.12,
+                     "rot": {"dims": rot_dim, "base": 10000.0, "scaling": scaling}}
+            kind = "latent_attention"
+        if window:
+            mixer["mask"] = {"size": window}
+        draw = rng.random()
+        if draw < 0.15:
+            mlp = None
+        elif draw < 0.55:
+            mlp = {"kind": "dense", "ff": rng.choice([64, 200, 320, 512])}
+        else:
+            groups, per = rng.choice([1, 2, 4]), rng.choice([2, 3, 4])
+            keep = rng.randint(1, groups)
+            router = {"experts": groups * per, "top": rng.randint(1, min(keep * per, 4))}
+            if groups > 1 or rng.random() < 0.5:
+                router["groups"] = {"count": groups, "keep": keep}
+            mlp = {"kind": "moe", "expert": {"ff": rng.choice([24, 64, 96, 128]), "limit": rng.choice([1.0, 3.0, 7.0])},
+                   "router": router}
+        layers.append({"type": kind, "mixer": mixer, "mlp": mlp})
+    config = {"architecture": "Kutolix", "vocab": rng.choice([300, 777, 1000]), "width": rng.choice([96, 128, 160, 256, 320]),
+              "norm": {"eps": 1e-5}, "layers": layers}
+    if rng.random() < 0.8:
+        config["embedding"] = {"scale": rng.choice([0.25, 2.0, 1.3])}
+    if rng.random() < 0.8:
+        config["residual_mult"] = rng.choice([0.4, 0.7, 1.5])
+    if rng.random() < 0.8:
+        config["logit_softcap"] = rng.choice([12.0, 30.0, 8.0])
+    return config
+
+
 def prompt(vocab: int, length: int, seed: int) -> list[int]:
     rng = random.Random(seed)
     return [rng.randrange(vocab) for _ in range(length)]
