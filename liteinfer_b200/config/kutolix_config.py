@@ -68,7 +68,7 @@ class KutolixMixer:
     kv_heads: int = 0                # attention
     rot_dim: int = 0                 # latent_attention: the rotated part of a query/key head
     kv_rank: int = 0                 # latent_attention: size of the latent
-    window: int | None = None        # position i sees j with 0 <= i - j < window
+    window: int | None = None        # a query at position p reads the keys at p - window + 1 ... p
     rot: KutolixRotation | None = None
 
     def __post_init__(self) -> None:

@@ -245,8 +245,8 @@ LI_EXPORT int li_latent_prep(int dtype, const void* proj, int proj_stride, int q
 // q_lat: the absorbed queries, head h of token t at q_lat + h * q_lat_head_stride + t * q_lat_token_stride
 // (kv_rank numbers).  q_raw: the query projection, the part of head h of token t that turns at
 // q_raw + t * q_raw_token_stride + h * q_raw_head_stride + q_rot_off (rot_dim numbers, not yet rotated).
-// out: like q_lat.  sink [heads] float or null.  window > 0: the query at position i sees the keys j with
-// 0 <= i - j < window.  cos_sin_scale multiplies every cosine and sine of the query's rotation.
+// out: like q_lat.  sink [heads] float or null.  window > 0: a query at position p reads the keys at
+// p - window + 1 ... p.  cos_sin_scale multiplies every cosine and sine of the query's rotation.
 LI_EXPORT int li_latent_attention(int dtype, const void* q_lat, long q_lat_head_stride, int q_lat_token_stride,
                                   const void* q_raw, int q_raw_token_stride, int q_raw_head_stride, int q_rot_off,
                                   void* out, long out_head_stride, int out_token_stride, const void* pool,

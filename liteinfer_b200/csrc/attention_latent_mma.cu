@@ -43,7 +43,7 @@ struct LatentParams {
   float* partial_lse;           // [splits][heads][tokens], in units of log2
   int tokens;
   int* error_flag;              // set to 31 if a wait for a tile of entries ever gave up (may be null)
-  int window;                   // > 0: the query at position i sees the keys j with 0 <= i - j < window
+  int window;                   // > 0: a query at position p reads the keys at p - window + 1 ... p
   float cs_scale;               // multiplies every cosine and sine of the query's rotation
 };
 

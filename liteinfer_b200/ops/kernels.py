@@ -1380,7 +1380,7 @@ def latent_attention(q_lat: torch.Tensor, q_raw: torch.Tensor, q_head_stride: in
     more term of the softmax's denominator (sink float32 [heads] or None).  q_lat, out: [heads, tokens, kv_rank];
     q_raw [tokens, columns]: the part of head h that turns lies at columns h * q_head_stride + q_rot_off (rot_dim
     numbers, rotated here by the query's position).  pool [pages, 1, page_size, kv_rank + rot_dim].  `window` > 0:
-    the query at position i sees the keys j with 0 <= i - j < window.  `cos_sin_scale` multiplies every cosine and
+    a query at position p reads the keys at p - window + 1 ... p.  `cos_sin_scale` multiplies every cosine and
     sine of the query's rotation."""
     _on_gpu(q_lat, out, pool, block_table, query_start_loc, context_lens, inv_freq, sink)
     _rows2d(q_raw, "q_raw")         # a column slice of a wider projection is fine

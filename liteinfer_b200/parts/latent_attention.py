@@ -19,7 +19,7 @@ schedule entry names (`cache_of`) with its own W_uk, W_uv and queries.  Rotation
 `rot.rotary_dim` numbers of the r-part; a position encoding whose checkpoint pairs neighbours has the rows of the
 rotated parts reordered when the tensors are bound, and one that stretches cosines and sines (YaRN) has its factor
 passed to the kernels.  `q_rank` None: no query latent, q = W_q h straight from the mixer's input.  `window`: the
-query at position i sees the keys j with 0 <= i - j < window, and the cache gives back the pages the window has
+query at position p reads the keys at p - window + 1 ... p, and the cache gives back the pages the window has
 passed.  Norms, angles, scores, softmax and the gate's sigmoid are 32-bit.
 """
 

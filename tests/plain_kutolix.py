@@ -91,7 +91,7 @@ def rotate(x, rot, layout):
 
 def windowed_softmax_attention(q, k, v, scale, window, sink=None):
     """q [T, H, D], k [T, H, D], v [T, H, V] (keys and values already per query head) -> [T, H, V].  Position i
-    sees j with 0 <= i - j < window (None: every j <= i).  `sink` [H]: exp(sink) joins the denominator."""
+    reads the keys at i - window + 1 ... i (None: every key up to i).  `sink` [H]: exp(sink) joins the denominator."""
     T, H, _ = q.shape
     out = torch.zeros(T, H, v.shape[2], dtype=F)
     for h in range(H):
